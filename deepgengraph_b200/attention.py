@@ -1,0 +1,178 @@
+"""Fused attention core modules on BSHD tensors.
+
+  attn_fwd(q, k, v, causal=True, window=-1, softcap=0.0, scale=None) -> out
+  attn_score_fwd(q, k, v, want_sq=False, ...)                       -> (out, colsum[, colsum_sq])
+  attn_kf_fwd(q, k, v, exp_rand, tau, ...)                          -> (out, kf_score)
+
+q [B, Sq, H, D], k/v [B, Skv, Hk, D] (fp16 or bf16, contiguous); outputs are freshly allocated
+on every call like the kernels the reference generates (to_triton.cpp:579-590): out [B, Sq, H, D]
+in the input dtype, score vectors float32 [B, Hk, Skv].
+
+The same three functions are registered as torch custom ops under the `b200attn` namespace
+(torch.ops.b200attn.attn_fwd, ...) with fake implementations, so that they can sit inside
+traced / compiled graphs.
+"""
+import math
+
+import torch
+
+from . import _lib
+from .native_ops import _dtype_code, _require_cuda, _stream_ptr
+
+
+def _check_qkv(where, q, k, v):
+  dev = _require_cuda(where, q, k, v)
+  if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+    raise ValueError(f"{where}: q, k, v must be [batch, seq, heads, head_dim]")
+  if q.dtype not in (torch.float16, torch.bfloat16) or k.dtype != q.dtype or v.dtype != q.dtype:
+    raise TypeError(f"{where}: q, k, v must share dtype float16 or bfloat16 (got {q.dtype}, {k.dtype}, {v.dtype})")
+  if k.shape != v.shape or k.size(0) != q.size(0) or k.size(3) != q.size(3):
+    raise ValueError(f"{where}: shape mismatch q={tuple(q.shape)} k={tuple(k.shape)} v={tuple(v.shape)}")
+  if q.size(2) % k.size(2) != 0:
+    raise ValueError(f"{where}: heads ({q.size(2)}) not a multiple of kv heads ({k.size(2)})")
+  if not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()):
+    raise ValueError(f"{where}: q, k, v must be contiguous")
+  return dev
+
+
+def _attn_fwd_impl(q, k, v, causal, window, softcap, scale, want_lse=False):
+  where = "attn_fwd"
+  dev = _check_qkv(where, q, k, v)
+  B, Sq, H, D = q.shape
+  Skv, Hk = k.size(1), k.size(2)
+  if scale is None or scale <= 0:
+    scale = 1.0 / math.sqrt(D)
+  out = torch.empty_like(q)
+  lse = torch.empty((B, H, Sq), dtype=torch.float32, device=dev) if want_lse else None
+  with torch.cuda.device(dev):
+    st = _lib.load().b200_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                   lse.data_ptr() if want_lse else None, B, Sq, Skv, H, Hk, D,
+                                   _dtype_code(q, where), int(bool(causal)), int(window), float(softcap),
+                                   float(scale), _stream_ptr(dev))
+  _lib.check(st, where)
+  return (out, lse) if want_lse else out
+
+
+def _workspace(dev, B, Sq, Skv, H):
+  nbytes = _lib.load().b200_attn_score_workspace_bytes(B, Sq, Skv, H)
+  return torch.empty(nbytes, dtype=torch.uint8, device=dev), nbytes
+
+
+def _attn_score_impl(q, k, v, want_sq, causal, window, softcap, scale):
+  where = "attn_score_fwd"
+  dev = _check_qkv(where, q, k, v)
+  B, Sq, H, D = q.shape
+  Skv, Hk = k.size(1), k.size(2)
+  if H != Hk:
+    raise ValueError(f"{where}: needs heads == kv heads (the reference asserts group_size == 1)")
+  if scale is None or scale <= 0:
+    scale = 1.0 / math.sqrt(D)
+  out = torch.empty_like(q)
+  score = torch.empty((B, H, Skv), dtype=torch.float32, device=dev)
+  score_sq = torch.empty((B, H, Skv), dtype=torch.float32, device=dev) if want_sq else None
+  ws, nbytes = _workspace(dev, B, Sq, Skv, H)
+  with torch.cuda.device(dev):
+    st = _lib.load().b200_attn_score(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), score.data_ptr(),
+                                     score_sq.data_ptr() if want_sq else None, ws.data_ptr(), nbytes, B, Sq, Skv, H,
+                                     D, _dtype_code(q, where), int(bool(causal)), int(window), float(softcap),
+                                     float(scale), _stream_ptr(dev))
+  _lib.check(st, where)
+  return (out, score, score_sq) if want_sq else (out, score)
+
+
+def _attn_kf_impl(q, k, v, exp_rand, tau, causal, scale):
+  where = "attn_kf_fwd"
+  dev = _check_qkv(where, q, k, v)
+  B, Sq, H, D = q.shape
+  Skv, Hk = k.size(1), k.size(2)
+  if H != Hk:
+    raise ValueError(f"{where}: needs heads == kv heads (the reference asserts group_size == 1)")
+  _require_cuda(where, q, exp_rand)
+  if exp_rand.dtype != torch.float32 or tuple(exp_rand.shape) != (B, H, Sq, Skv) or not exp_rand.is_contiguous():
+    raise ValueError(f"{where}: exp_rand must be contiguous float32 [batch, heads, q_len, kv_len]")
+  if scale is None or scale <= 0:
+    scale = 1.0 / math.sqrt(D)
+  out = torch.empty_like(q)
+  score = torch.empty((B, H, Skv), dtype=torch.float32, device=dev)
+  ws, nbytes = _workspace(dev, B, Sq, Skv, H)
+  with torch.cuda.device(dev):
+    st = _lib.load().b200_attn_kf_score(q.data_ptr(), k.data_ptr(), v.data_ptr(), exp_rand.data_ptr(),
+                                        out.data_ptr(), score.data_ptr(), ws.data_ptr(), nbytes, B, Sq, Skv, H, D,
+                                        _dtype_code(q, where), int(bool(causal)), float(tau), float(scale),
+                                        _stream_ptr(dev))
+  _lib.check(st, where)
+  return out, score
+
+
+# ----------------------------------------------------------------------------------------------
+# torch custom ops (namespace b200attn) with fake kernels for tracing
+# ----------------------------------------------------------------------------------------------
+@torch.library.custom_op("b200attn::attn_fwd", mutates_args=())
+def _op_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool, window: int, softcap: float,
+                 scale: float) -> torch.Tensor:
+  return _attn_fwd_impl(q, k, v, causal, window, softcap, scale)
+
+
+@_op_attn_fwd.register_fake
+def _(q, k, v, causal, window, softcap, scale):
+  return torch.empty_like(q)
+
+
+@torch.library.custom_op("b200attn::attn_score_fwd", mutates_args=())
+def _op_attn_score_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool, window: int, softcap: float,
+                       scale: float) -> tuple[torch.Tensor, torch.Tensor]:
+  return _attn_score_impl(q, k, v, False, causal, window, softcap, scale)
+
+
+@_op_attn_score_fwd.register_fake
+def _(q, k, v, causal, window, softcap, scale):
+  return torch.empty_like(q), q.new_empty((q.size(0), k.size(2), k.size(1)), dtype=torch.float32)
+
+
+@torch.library.custom_op("b200attn::attn_score_sq_fwd", mutates_args=())
+def _op_attn_score_sq_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool, window: int,
+                          softcap: float, scale: float) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+  return _attn_score_impl(q, k, v, True, causal, window, softcap, scale)
+
+
+@_op_attn_score_sq_fwd.register_fake
+def _(q, k, v, causal, window, softcap, scale):
+  s = q.new_empty((q.size(0), k.size(2), k.size(1)), dtype=torch.float32)
+  return torch.empty_like(q), s, torch.empty_like(s)
+
+
+@torch.library.custom_op("b200attn::attn_kf_fwd", mutates_args=())
+def _op_attn_kf_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, exp_rand: torch.Tensor, tau: float,
+                    causal: bool, scale: float) -> tuple[torch.Tensor, torch.Tensor]:
+  return _attn_kf_impl(q, k, v, exp_rand, tau, causal, scale)
+
+
+@_op_attn_kf_fwd.register_fake
+def _(q, k, v, exp_rand, tau, causal, scale):
+  return torch.empty_like(q), q.new_empty((q.size(0), k.size(2), k.size(1)), dtype=torch.float32)
+
+
+# ----------------------------------------------------------------------------------------------
+# public functions
+# ----------------------------------------------------------------------------------------------
+def attn_fwd(q, k, v, causal=True, window=-1, softcap=0.0, scale=None):
+  """softmax(mask(softcap(q k^T * scale))) v   (kernels/attn.py:18-34, kernels/gemma2.py:19-38)."""
+  return _op_attn_fwd(q, k, v, bool(causal), int(window), float(softcap), float(scale or 0.0))
+
+
+def attn_fwd_with_lse(q, k, v, causal=True, window=-1, softcap=0.0, scale=None):
+  """attn_fwd plus the base-2 log-sum-exp of every row of scaled logits, float32 [B, H, Sq]."""
+  return _attn_fwd_impl(q, k, v, causal, window, softcap, scale, want_lse=True)
+
+
+def attn_score_fwd(q, k, v, want_sq=False, causal=True, window=-1, softcap=0.0, scale=None):
+  """Attention output + per-key column sums of the fp32 probabilities (kernels/h2o.py:35-38);
+  want_sq adds the column sums of the squared probabilities (kernels/roco.py:42-48)."""
+  op = _op_attn_score_sq_fwd if want_sq else _op_attn_score_fwd
+  return op(q, k, v, bool(causal), int(window), float(softcap), float(scale or 0.0))
+
+
+def attn_kf_fwd(q, k, v, exp_rand, tau=1.5, causal=True, scale=None):
+  """Attention output + KeyFormer score: column sums of softmax((logits - log(exp_rand)) / tau)
+  (kernels/kf.py:36-42)."""
+  return _op_attn_kf_fwd(q, k, v, exp_rand, float(tau), bool(causal), float(scale or 0.0))

@@ -1,0 +1,520 @@
+// Fused attention forward for sm_100a:  out = softmax(mask(softcap(q k^T * scale))) v.
+//
+// One CTA owns NQ query tiles of 128 rows of one (batch, head) and walks the key/value
+// blocks that the causal / sliding-window mask leaves visible.  Roles (warp-specialised):
+//   warps [0, 4*NQ)   softmax warpgroups, one per query tile: thread r of a group owns row r
+//                     (TMEM lane r) -- online softmax, O rescale, epilogue
+//   warp  4*NQ        TMA producer (one lane): Q once, then a ring of K and V stages
+//   warp  4*NQ + 1    MMA issuer (one lane): S = Q K^T (operands in shared memory) and
+//                     O += P V (P read from TMEM, V from shared memory) on tcgen05
+// TMEM columns: [S tile per query tile (fp32, BN columns; the 16-bit P overwrites its first
+// BN/2 columns)] [O accumulator per query tile (fp32, D columns)].
+//
+// Reference semantics: deepgengraph_exp/cases/kernels/attn.py:18-34 (mask, scale, fp32
+// softmax, P rounded to the input type before P V) and kernels/gemma2.py:30-34 (soft-cap
+// after the scale, before the mask).
+#pragma once
+
+#include "common.cuh"
+
+namespace b200 {
+
+struct FwdParams {
+  void* out;    // [B, Sq, H, D]
+  float* lse;   // [B*H][lse_stride] base-2 log-sum-exp of the scaled logits, may be null
+  int lse_stride;
+  int batch, q_len, kv_len, heads, kv_heads;
+  int causal, window;
+  int delta;          // kv_len - q_len
+  float scale_log2;   // scale * log2(e)              (no soft-cap)
+  float cap_in;       // scale / softcap              (soft-cap: x = tanh(s * cap_in) * cap_out)
+  float cap_out;      // softcap * log2(e)
+};
+
+template <int D_, int BN_, int NQ_>
+struct FwdCfg {
+  static constexpr int D = D_, BN = BN_, NQ = NQ_;
+  static constexpr int BM = 128;
+  static constexpr int STAGES = 2;
+  static constexpr int KSUB = D / 64;                 // 64-element (128-byte) column blocks of a row
+  static constexpr int Q_TILE_BYTES = BM * D * 2;
+  static constexpr int KV_STAGE_BYTES = BN * D * 2;
+  static constexpr int O_BASE = ((NQ * BN + D - 1) / D) * D;
+  static constexpr int TMEM_USED = O_BASE + NQ * D;
+  static constexpr int TMEM_COLS = TMEM_USED <= 32 ? 32 : TMEM_USED <= 64 ? 64 : TMEM_USED <= 128 ? 128
+                                   : TMEM_USED <= 256 ? 256 : 512;
+  static_assert(TMEM_USED <= 512, "TMEM budget exceeded");
+  static constexpr int THREADS = (NQ * 4 + 2) * 32;
+  // barrier slots
+  static constexpr int BAR_Q_FULL = 0;                       // [NQ]
+  static constexpr int BAR_S_FULL = BAR_Q_FULL + NQ;         // [NQ]
+  static constexpr int BAR_P_FULL = BAR_S_FULL + NQ;         // [NQ]
+  static constexpr int BAR_O_FULL = BAR_P_FULL + NQ;         // [NQ]
+  static constexpr int BAR_K_FULL = BAR_O_FULL + NQ;         // [STAGES]
+  static constexpr int BAR_K_EMPTY = BAR_K_FULL + STAGES;
+  static constexpr int BAR_V_FULL = BAR_K_EMPTY + STAGES;
+  static constexpr int BAR_V_EMPTY = BAR_V_FULL + STAGES;
+  static constexpr int BAR_DRAIN = BAR_V_EMPTY + STAGES;
+  static constexpr int NUM_BARS = BAR_DRAIN + 1;
+  static constexpr int SMEM_TILES = NQ * Q_TILE_BYTES + 2 * STAGES * KV_STAGE_BYTES;
+  static constexpr int SMEM_BYTES = SMEM_TILES + NUM_BARS * 8 + 16 + 1024;  // +1024: manual alignment slack
+};
+
+// Block range of one query tile: key blocks [lo, hi) hold at least one visible key.
+struct TileRange {
+  int lo, hi;
+};
+__device__ __forceinline__ TileRange tile_range(int r_first, int bn, const FwdParams& p) {
+  TileRange r;
+  if (r_first >= p.q_len) {
+    r.lo = r.hi = 0;
+    return r;
+  }
+  const int r_last = min(r_first + 127, p.q_len - 1);
+  const int last_key = p.causal ? min(p.kv_len - 1, r_last + p.delta) : p.kv_len - 1;
+  r.hi = last_key / bn + 1;
+  r.lo = (p.causal && p.window > 0) ? max(0, r_first + p.delta - p.window + 1) / bn : 0;
+  return r;
+}
+
+template <class Cfg, bool BF16>
+struct FwdCtx {
+  uint8_t* sQ;
+  uint8_t* sK;
+  uint8_t* sV;
+  uint64_t* bars;
+  volatile int* abort_flag;
+  uint32_t tmem_base;
+  int q0, h, hk, b;
+  TileRange rng[Cfg::NQ];
+  int jmin, jmax;
+};
+
+// ------------------------------- TMA producer -------------------------------
+template <class Cfg, bool BF16>
+__device__ __forceinline__ void fwd_producer(const FwdCtx<Cfg, BF16>& c, const CUtensorMap* tm_q,
+                                             const CUtensorMap* tm_k, const CUtensorMap* tm_v) {
+  constexpr int ST = Cfg::STAGES;
+#pragma unroll
+  for (int t = 0; t < Cfg::NQ; ++t) {
+    if (c.rng[t].hi > c.rng[t].lo) {
+      mbar_expect_tx(&c.bars[Cfg::BAR_Q_FULL + t], Cfg::Q_TILE_BYTES);
+#pragma unroll
+      for (int ks = 0; ks < Cfg::KSUB; ++ks)
+        tma_load_4d(c.sQ + t * Cfg::Q_TILE_BYTES + ks * (Cfg::BM * 128), tm_q, &c.bars[Cfg::BAR_Q_FULL + t],
+                    ks * 64, c.h, c.q0 + t * Cfg::BM, c.b);
+    }
+  }
+  int issued = 0;
+  bool ok = true;
+  for (int j = c.jmin; j < c.jmax && ok; ++j) {
+    const int n = j - c.jmin, st = n % ST, use = n / ST;
+    if (use > 0) ok = mbar_wait(&c.bars[Cfg::BAR_K_EMPTY + st], (use - 1) & 1, c.abort_flag, WAIT_K_EMPTY);
+    if (!ok) break;
+    mbar_expect_tx(&c.bars[Cfg::BAR_K_FULL + st], Cfg::KV_STAGE_BYTES);
+#pragma unroll
+    for (int ks = 0; ks < Cfg::KSUB; ++ks)
+      tma_load_4d(c.sK + st * Cfg::KV_STAGE_BYTES + ks * (Cfg::BN * 128), tm_k, &c.bars[Cfg::BAR_K_FULL + st],
+                  ks * 64, c.hk, j * Cfg::BN, c.b);
+    if (use > 0) ok = mbar_wait(&c.bars[Cfg::BAR_V_EMPTY + st], (use - 1) & 1, c.abort_flag, WAIT_V_EMPTY);
+    if (!ok) {
+      issued = n * 2 + 1;
+      break;
+    }
+    mbar_expect_tx(&c.bars[Cfg::BAR_V_FULL + st], Cfg::KV_STAGE_BYTES);
+#pragma unroll
+    for (int ks = 0; ks < Cfg::KSUB; ++ks)
+      tma_load_4d(c.sV + st * Cfg::KV_STAGE_BYTES + ks * (Cfg::BN * 128), tm_v, &c.bars[Cfg::BAR_V_FULL + st],
+                  ks * 64, c.hk, j * Cfg::BN, c.b);
+    issued = n * 2 + 2;
+  }
+  if (!ok || *c.abort_flag != 0) {
+    // Abort path: do not leave the CTA while our own bulk copies may still be landing in
+    // shared memory.  Wait (bounded, 20 ms) for the most recent load of every stage.
+    const uint64_t t0 = global_timer_ns();
+    const int nk = (issued + 1) / 2, nv = issued / 2;  // K loads, V loads issued
+    for (int st = 0; st < ST; ++st) {
+      const int uk = (nk - 1 - st) >= 0 ? (nk - 1 - st) / ST : -1;  // last use index of stage st for K
+      const int uv = (nv - 1 - st) >= 0 ? (nv - 1 - st) / ST : -1;
+      while (uk >= 0 && !mbar_try_wait(&c.bars[Cfg::BAR_K_FULL + st], uk & 1) &&
+             global_timer_ns() - t0 < 20000000ull) {
+      }
+      while (uv >= 0 && !mbar_try_wait(&c.bars[Cfg::BAR_V_FULL + st], uv & 1) &&
+             global_timer_ns() - t0 < 20000000ull) {
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < Cfg::NQ; ++t)
+      while (c.rng[t].hi > c.rng[t].lo && !mbar_try_wait(&c.bars[Cfg::BAR_Q_FULL + t], 0) &&
+             global_timer_ns() - t0 < 20000000ull) {
+      }
+  }
+}
+
+// -------------------------------- MMA issuer --------------------------------
+template <class Cfg, bool BF16>
+__device__ __forceinline__ void fwd_mma(const FwdCtx<Cfg, BF16>& c) {
+  constexpr int ST = Cfg::STAGES, D = Cfg::D, BN = Cfg::BN, BM = Cfg::BM, NQ = Cfg::NQ;
+  constexpr uint32_t IDESC_S = make_idesc(BF16, BM, BN, false, false);
+  constexpr uint32_t IDESC_PV = make_idesc(BF16, BM, D, false, true);
+  const uint32_t q_addr = smem_u32(c.sQ), k_addr = smem_u32(c.sK), v_addr = smem_u32(c.sV);
+  int k_ready = c.jmin - 1, v_ready = c.jmin - 1;  // last block whose K / V stage has been observed full
+  bool ok = true;
+
+  auto issue_s = [&](int t, int j) {
+    const int n = j - c.jmin, st = n % ST;
+    if (j == c.rng[t].lo) ok = ok && mbar_wait(&c.bars[Cfg::BAR_Q_FULL + t], 0, c.abort_flag, WAIT_Q_FULL);
+    if (ok && k_ready < j) {
+      ok = mbar_wait(&c.bars[Cfg::BAR_K_FULL + st], (n / ST) & 1, c.abort_flag, WAIT_K_FULL);
+      k_ready = j;
+    }
+    if (!ok) return;
+    tc_fence_after();
+    const uint32_t d_tmem = c.tmem_base + t * BN;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      const uint64_t a = make_smem_desc(q_addr + t * Cfg::Q_TILE_BYTES + (kk / 4) * (BM * 128) + (kk % 4) * 32, 16, 1024);
+      const uint64_t bdesc = make_smem_desc(k_addr + st * Cfg::KV_STAGE_BYTES + (kk / 4) * (BN * 128) + (kk % 4) * 32, 16, 1024);
+      umma_ss(d_tmem, a, bdesc, IDESC_S, kk > 0 ? 1u : 0u);
+    }
+    umma_commit(&c.bars[Cfg::BAR_S_FULL + t]);
+  };
+  auto issue_pv = [&](int t, int j) {
+    const int n = j - c.jmin, st = n % ST;
+    ok = ok && mbar_wait(&c.bars[Cfg::BAR_P_FULL + t], (j - c.rng[t].lo) & 1, c.abort_flag, WAIT_P_FULL);
+    if (ok && v_ready < j) {
+      ok = mbar_wait(&c.bars[Cfg::BAR_V_FULL + st], (n / ST) & 1, c.abort_flag, WAIT_V_FULL);
+      v_ready = j;
+    }
+    if (!ok) return;
+    tc_fence_after();
+    const uint32_t d_tmem = c.tmem_base + Cfg::O_BASE + t * D;
+    const uint32_t a_tmem = c.tmem_base + t * BN;  // P: packed 16-bit pairs, 8 columns per 16 keys
+#pragma unroll
+    for (int kk = 0; kk < BN / 16; ++kk) {
+      // V stage: KSUB column blocks of [BN keys][64 dims]; MN-major B operand
+      const uint64_t bdesc = make_smem_desc(v_addr + st * Cfg::KV_STAGE_BYTES + kk * 2048, BN * 128, 1024);
+      umma_ts(d_tmem, a_tmem + kk * 8, bdesc, IDESC_PV, (j > c.rng[t].lo || kk > 0) ? 1u : 0u);
+    }
+    umma_commit(&c.bars[Cfg::BAR_O_FULL + t]);
+  };
+  auto active = [&](int t, int j) { return j >= c.rng[t].lo && j < c.rng[t].hi; };
+
+  // prologue: S of the first block
+#pragma unroll
+  for (int t = 0; t < NQ; ++t)
+    if (ok && active(t, c.jmin)) issue_s(t, c.jmin);
+  if (ok && c.jmax > c.jmin) umma_commit(&c.bars[Cfg::BAR_K_EMPTY + 0]);
+
+  for (int j = c.jmin; j < c.jmax && ok; ++j) {
+    const int n = j - c.jmin;
+#pragma unroll
+    for (int t = 0; t < NQ; ++t) {
+      if (ok && active(t, j)) issue_pv(t, j);
+      if (ok && active(t, j + 1)) issue_s(t, j + 1);
+    }
+    if (!ok) break;
+    umma_commit(&c.bars[Cfg::BAR_V_EMPTY + n % ST]);                          // V(j) consumed
+    if (j + 1 < c.jmax) umma_commit(&c.bars[Cfg::BAR_K_EMPTY + (n + 1) % ST]);  // K(j+1) consumed
+  }
+  // every MMA issued above has retired before the CTA tears TMEM down
+  umma_commit(&c.bars[Cfg::BAR_DRAIN]);
+  mbar_wait(&c.bars[Cfg::BAR_DRAIN], 0, c.abort_flag, WAIT_DRAIN);
+}
+
+// ------------------------------ softmax warpgroup ----------------------------
+template <class Cfg, bool BF16, bool SOFTCAP>
+__device__ __forceinline__ void fwd_softmax(const FwdCtx<Cfg, BF16>& c, const FwdParams& p, int t) {
+  constexpr int D = Cfg::D, BN = Cfg::BN;
+  const int warp_q = (threadIdx.x >> 5) & 3, lane = threadIdx.x & 31;
+  const TileRange rng = c.rng[t];
+  if (rng.hi <= rng.lo) return;
+  const int r_tile = c.q0 + t * Cfg::BM;
+  const int row = r_tile + warp_q * 32 + lane;
+  const uint32_t lane_addr = c.tmem_base + ((uint32_t)(warp_q * 32) << 16);
+  const uint32_t s_addr = lane_addr + t * BN;
+  const uint32_t o_addr = lane_addr + Cfg::O_BASE + t * D;
+  uint64_t* s_full = &c.bars[Cfg::BAR_S_FULL + t];
+  uint64_t* p_full = &c.bars[Cfg::BAR_P_FULL + t];
+  uint64_t* o_full = &c.bars[Cfg::BAR_O_FULL + t];
+
+  const float cmul = SOFTCAP ? 1.0f : p.scale_log2;
+  float m = -1.0e30f;  // running reference maximum (base-2 units); finite so that fully masked blocks stay NaN-free
+  float l = 0.f;
+
+  for (int j = rng.lo; j < rng.hi; ++j) {
+    const int n = j - rng.lo;
+    if (!mbar_wait(s_full, n & 1, c.abort_flag, WAIT_S_FULL)) return;
+    tc_fence_after();
+    uint32_t sr[BN / 32][32];
+#pragma unroll
+    for (int ch = 0; ch < BN / 32; ++ch) tmem_ld32(s_addr + ch * 32, sr[ch]);
+    tmem_ld_wait();
+
+    // visible columns of this row inside the block: [lo_c, hi_c]
+    const int hi_key = p.causal ? min(row + p.delta, p.kv_len - 1) : p.kv_len - 1;
+    const int hi_c = hi_key - j * BN;
+    const int lo_c = (p.causal && p.window > 0) ? (row + p.delta - p.window + 1 - j * BN) : -(1 << 28);
+    const int hi_first = (p.causal ? min(r_tile + p.delta, p.kv_len - 1) : p.kv_len - 1) - j * BN;
+    const bool need_mask = (hi_first < BN - 1) ||
+                           (p.causal && p.window > 0 && (r_tile + 127 + p.delta - p.window + 1 - j * BN) > 0);
+
+    float mx = -INFINITY;
+#pragma unroll
+    for (int ch = 0; ch < BN / 32; ++ch) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        float s = __uint_as_float(sr[ch][i]);
+        if constexpr (SOFTCAP) s = tanh_approx(s * p.cap_in) * p.cap_out;
+        if (need_mask) {
+          const int col = ch * 32 + i;
+          if (col > hi_c || col < lo_c) s = -INFINITY;
+        }
+        sr[ch][i] = __float_as_uint(s);
+        mx = fmaxf(mx, s);
+      }
+    }
+    const float m_blk = mx * cmul;  // -inf when the whole row is masked inside this block
+    float alpha = 1.0f;
+    bool rescale = false;
+    if (n == 0) {
+      m = fmaxf(m, m_blk);
+    } else if (m_blk - m > 8.0f) {
+      // Lazy rescale: the running reference only moves when the new maximum exceeds it by more
+      // than 2^8, so that exp2(x - m) stays <= 256 and O is touched rarely.
+      alpha = ex2_approx(m - m_blk);
+      m = m_blk;
+      l *= alpha;
+      rescale = true;
+    }
+    if (n > 0 && __any_sync(0xffffffffu, rescale)) {
+      if (!mbar_wait(o_full, (n - 1) & 1, c.abort_flag, WAIT_O_FULL)) return;
+      tc_fence_after();
+#pragma unroll
+      for (int ch = 0; ch < D / 32; ++ch) {
+        uint32_t o[32];
+        tmem_ld32(o_addr + ch * 32, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+        tmem_st32(o_addr + ch * 32, o);
+      }
+    }
+    // P = exp2(x - m), packed to the 16-bit input type, written over the first BN/2 columns of S
+    const float neg_m = -m;
+    float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#pragma unroll
+    for (int ch = 0; ch < BN / 64; ++ch) {
+      uint32_t pk[32];
+#pragma unroll
+      for (int i = 0; i < 64; i += 4) {
+        const float p0 = ex2_approx(fmaf(__uint_as_float(sr[ch * 2 + i / 32][(i + 0) % 32]), cmul, neg_m));
+        const float p1 = ex2_approx(fmaf(__uint_as_float(sr[ch * 2 + i / 32][(i + 1) % 32]), cmul, neg_m));
+        const float p2 = ex2_approx(fmaf(__uint_as_float(sr[ch * 2 + i / 32][(i + 2) % 32]), cmul, neg_m));
+        const float p3 = ex2_approx(fmaf(__uint_as_float(sr[ch * 2 + i / 32][(i + 3) % 32]), cmul, neg_m));
+        l0 += p0;
+        l1 += p1;
+        l2 += p2;
+        l3 += p3;
+        pk[i / 2] = pack2<BF16>(p0, p1);
+        pk[i / 2 + 1] = pack2<BF16>(p2, p3);
+      }
+      tmem_st32(s_addr + ch * 32, pk);
+    }
+    l += (l0 + l1) + (l2 + l3);
+    tmem_st_wait();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(p_full);
+  }
+
+  // epilogue: O / l -> 16-bit -> global (BSHD), base-2 LSE for the score passes
+  if (!mbar_wait(o_full, (rng.hi - rng.lo - 1) & 1, c.abort_flag, WAIT_O_FULL)) return;
+  tc_fence_after();
+  const float inv_l = 1.0f / l;
+  const bool in_range = row < p.q_len;
+  uint4* out_row = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) +
+                                            (((int64_t)c.b * p.q_len + row) * p.heads + c.h) * (int64_t)D);
+#pragma unroll
+  for (int ch = 0; ch < D / 32; ++ch) {
+    uint32_t o[32];
+    tmem_ld32(o_addr + ch * 32, o);
+    tmem_ld_wait();
+    if (in_range) {
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        uint4 w;
+        w.x = pack2<BF16>(__uint_as_float(o[v * 8 + 0]) * inv_l, __uint_as_float(o[v * 8 + 1]) * inv_l);
+        w.y = pack2<BF16>(__uint_as_float(o[v * 8 + 2]) * inv_l, __uint_as_float(o[v * 8 + 3]) * inv_l);
+        w.z = pack2<BF16>(__uint_as_float(o[v * 8 + 4]) * inv_l, __uint_as_float(o[v * 8 + 5]) * inv_l);
+        w.w = pack2<BF16>(__uint_as_float(o[v * 8 + 6]) * inv_l, __uint_as_float(o[v * 8 + 7]) * inv_l);
+        out_row[ch * 4 + v] = w;
+      }
+    }
+  }
+  if (p.lse != nullptr && in_range) p.lse[((int64_t)c.b * p.heads + c.h) * p.lse_stride + row] = m + log2f(l);
+}
+
+// ----------------------------------- kernel ----------------------------------
+template <int D, int BN, int NQ, bool BF16, bool SOFTCAP>
+__global__ void __launch_bounds__(FwdCfg<D, BN, NQ>::THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
+  using Cfg = FwdCfg<D, BN, NQ>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+
+  // A launch that follows an expired wait on this device drains immediately (the status word stays
+  // set until the host reads it), so that one stuck kernel cannot stall a whole queue of launches.
+  __shared__ int s_skip;
+  if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(&g_device_status);
+  __syncthreads();
+  if (s_skip != 0) return;
+
+  FwdCtx<Cfg, BF16> c;
+  c.sQ = smem;
+  c.sK = c.sQ + NQ * Cfg::Q_TILE_BYTES;
+  c.sV = c.sK + Cfg::STAGES * Cfg::KV_STAGE_BYTES;
+  c.bars = reinterpret_cast<uint64_t*>(c.sV + Cfg::STAGES * Cfg::KV_STAGE_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(c.bars + Cfg::NUM_BARS);
+  c.abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // heaviest query groups (largest row index => most visible key blocks) are scheduled first
+  const int qg = gridDim.x - 1 - blockIdx.x;
+  c.q0 = qg * Cfg::BM * NQ;
+  c.h = blockIdx.y;
+  c.b = blockIdx.z;
+  c.hk = c.h / (p.heads / p.kv_heads);
+  c.jmin = 1 << 30;
+  c.jmax = 0;
+#pragma unroll
+  for (int t = 0; t < NQ; ++t) {
+    c.rng[t] = tile_range(c.q0 + t * Cfg::BM, BN, p);
+    if (c.rng[t].hi > c.rng[t].lo) {
+      c.jmin = min(c.jmin, c.rng[t].lo);
+      c.jmax = max(c.jmax, c.rng[t].hi);
+    }
+  }
+  if (c.jmax == 0) c.jmin = 0;
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int i = 0; i < Cfg::NUM_BARS; ++i) {
+      const bool is_p_full = (i >= Cfg::BAR_P_FULL && i < Cfg::BAR_P_FULL + NQ);
+      mbar_init(&c.bars[i], is_p_full ? 4u : 1u);
+    }
+    *c.abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == NQ * 4 && lane == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  c.tmem_base = *tmem_slot;
+
+  if (warp < NQ * 4) {
+    fwd_softmax<Cfg, BF16, SOFTCAP>(c, p, warp >> 2);
+  } else if (warp == NQ * 4) {
+    if (lane == 0) fwd_producer<Cfg, BF16>(c, &tm_q, &tm_k, &tm_v);
+  } else {
+    if (lane == 0) fwd_mma<Cfg, BF16>(c);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(c.tmem_base, Cfg::TMEM_COLS);
+}
+
+// --------------------------------- host side ---------------------------------
+template <int D, int BN, int NQ, bool BF16, bool SOFTCAP>
+int launch_attn_fwd_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
+                        cudaStream_t stream) {
+  using Cfg = FwdCfg<D, BN, NQ>;
+  auto kern = attn_fwd_kernel<D, BN, NQ, BF16, SOFTCAP>;
+  static thread_local int configured_dev = -1;
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (configured_dev != dev) {
+    B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    configured_dev = dev;
+  }
+  const int groups = (p.q_len + Cfg::BM * NQ - 1) / (Cfg::BM * NQ);
+  dim3 grid(groups, p.heads, p.batch);
+  kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+inline int attn_fwd_impl_lse_stride(const void* q, const void* k, const void* v, void* out, float* lse,
+                                    int lse_stride, int batch, int q_len, int kv_len, int heads, int kv_heads,
+                                    int head_dim, int dtype, int causal, int window, float softcap, float scale,
+                                    cudaStream_t stream) {
+  if (!q || !k || !v || !out) return B200_ERR_BAD_ARGUMENT;
+  if (batch <= 0 || q_len <= 0 || kv_len <= 0 || heads <= 0 || kv_heads <= 0) return B200_ERR_BAD_ARGUMENT;
+  if (dtype != B200_F16 && dtype != B200_BF16) return B200_ERR_BAD_DTYPE;
+  if (head_dim != 128 && head_dim != 256) return B200_ERR_UNSUPPORTED;
+  if (heads % kv_heads != 0) return B200_ERR_BAD_ARGUMENT;
+  if (kv_len < q_len) return B200_ERR_UNSUPPORTED;  // rows without any visible key (the reference yields NaN)
+  if (window > 0 && !causal) return B200_ERR_UNSUPPORTED;
+  if (!(scale > 0.f) || softcap < 0.f) return B200_ERR_BAD_ARGUMENT;
+  if (heads > 65535 || batch > 65535) return B200_ERR_UNSUPPORTED;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return B200_ERR_MISALIGNED;
+
+  const bool bf16 = dtype == B200_BF16;
+  const int bn = head_dim == 128 ? 128 : 64;
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = make_bshd_tensor_map(&tq, q, batch, q_len, heads, head_dim, 128, bf16)) != B200_OK) return rc;
+  if ((rc = make_bshd_tensor_map(&tk, k, batch, kv_len, kv_heads, head_dim, bn, bf16)) != B200_OK) return rc;
+  if ((rc = make_bshd_tensor_map(&tv, v, batch, kv_len, kv_heads, head_dim, bn, bf16)) != B200_OK) return rc;
+
+  FwdParams p;
+  p.out = out;
+  p.lse = lse;
+  p.lse_stride = lse_stride;
+  p.batch = batch;
+  p.q_len = q_len;
+  p.kv_len = kv_len;
+  p.heads = heads;
+  p.kv_heads = kv_heads;
+  p.causal = causal ? 1 : 0;
+  p.window = window > 0 ? window : 0;
+  p.delta = kv_len - q_len;
+  const float kLog2e = 1.4426950408889634f;
+  p.scale_log2 = scale * kLog2e;
+  p.cap_in = softcap > 0.f ? scale / softcap : 0.f;
+  p.cap_out = softcap * kLog2e;
+  const bool cap = softcap > 0.f;
+
+#define B200_FWD_DISPATCH(D_, BN_, NQ_)                                                                      \
+  (bf16 ? (cap ? launch_attn_fwd_cfg<D_, BN_, NQ_, true, true>(tq, tk, tv, p, stream)                        \
+               : launch_attn_fwd_cfg<D_, BN_, NQ_, true, false>(tq, tk, tv, p, stream))                      \
+        : (cap ? launch_attn_fwd_cfg<D_, BN_, NQ_, false, true>(tq, tk, tv, p, stream)                       \
+               : launch_attn_fwd_cfg<D_, BN_, NQ_, false, false>(tq, tk, tv, p, stream)))
+  if (head_dim == 128) {
+    // two query tiles per CTA keep the tensor pipe busy while one tile is in its softmax;
+    // short sequences use one tile per CTA so that more CTAs exist
+    if (q_len > 128) return B200_FWD_DISPATCH(128, 128, 2);
+    return B200_FWD_DISPATCH(128, 128, 1);
+  }
+  return B200_FWD_DISPATCH(256, 64, 1);
+#undef B200_FWD_DISPATCH
+}
+
+inline int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, float* lse, int batch, int q_len,
+                         int kv_len, int heads, int kv_heads, int head_dim, int dtype, int causal, int window,
+                         float softcap, float scale, cudaStream_t stream) {
+  return attn_fwd_impl_lse_stride(q, k, v, out, lse, q_len, batch, q_len, kv_len, heads, kv_heads, head_dim, dtype,
+                                  causal, window, softcap, scale, stream);
+}
+
+}  // namespace b200

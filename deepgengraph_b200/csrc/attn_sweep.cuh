@@ -1,0 +1,625 @@
+// Score sweeps for the fine-grained-property variants (H2O / RoCo / KeyFormer).
+//
+// The per-key statistics need the FINAL softmax normaliser of every query row, so they are a
+// second sweep over the logits after the forward kernel has produced the base-2 log-sum-exp of
+// each row.  The sweep keeps one 128-row tile stationary in shared memory and streams blocks
+// of the other operand through a TMA ring; the tile product lands in TMEM (double buffered)
+// with the STATIONARY rows on the TMEM lanes, so that every thread of the compute warpgroup
+// owns one stationary row and reduces along the streamed dimension in registers:
+//
+//   SWEEP_COLSUM     stationary = 128 keys,    streamed = query blocks.
+//                    thread j accumulates sum_i p_ij (and sum_i p_ij^2): no cross-thread
+//                    reduction at all.  Query blocks are split into chunks over CTAs; each CTA
+//                    writes one partial vector and a small pass adds the partials in a fixed
+//                    order (no atomics, bit-reproducible).
+//                    -- H2O.forward kernels/h2o.py:35-38, RoCo.forward kernels/roco.py:42-48
+//   SWEEP_KF_COLSUM  same, with p2_ij = exp2((x_ij - log2 e_ij) / tau - Lz_i), e = exp_rand
+//                    -- KeyFormer.forward kernels/kf.py:36-42
+//   SWEEP_KF_ROWLSE  stationary = 128 queries, streamed = key blocks; thread i runs an online
+//                    log-sum-exp of z_ij = (x_ij - log2 e_ij) / tau over the keys -> Lz_i.
+//
+// x_ij are the scaled (and soft-capped) logits in base-2 units, exactly as in the forward kernel.
+#pragma once
+
+#include "common.cuh"
+#include "attn_fwd.cuh"
+
+namespace b200 {
+
+enum SweepMode : int { SWEEP_COLSUM = 0, SWEEP_KF_COLSUM = 1, SWEEP_KF_ROWLSE = 2 };
+
+struct SweepParams {
+  const float* lse;     // [B*H][lse_stride]  row normalisers (COLSUM: L, KF_COLSUM: Lz)
+  float* lse_out;       // [B*H][lse_stride]  KF_ROWLSE output
+  float* partial;       // [B*H][n_chunks][kv_pad]
+  float* partial_sq;    // same shape, RoCo only
+  int batch, heads, q_len, kv_len, delta, causal, window;
+  int lse_stride, kv_pad, n_chunks, chunk_blocks;
+  float scale_log2, cap_in, cap_out, inv_tau;
+};
+
+template <int MODE_, int BX_, int STAGES_>
+struct SweepCfg {
+  static constexpr int MODE = MODE_, BX = BX_, STAGES = STAGES_;
+  static constexpr int D = 128, BM = 128;
+  static constexpr bool NOISE = MODE != SWEEP_COLSUM;
+  static constexpr bool LSE_IN = MODE != SWEEP_KF_ROWLSE;
+  static constexpr int A_BYTES = BM * D * 2;
+  static constexpr int X_STAGE_BYTES = BX * D * 2;
+  static constexpr int NOISE_BYTES = NOISE ? BM * BX * 4 : 0;
+  static constexpr int LSE_BYTES = LSE_IN ? BX * 4 : 0;
+  static constexpr int N_STAGE_BYTES = NOISE_BYTES + LSE_BYTES;       // auxiliary ring read by the compute warps
+  static constexpr int N_STAGE_STRIDE = (N_STAGE_BYTES + 1023) / 1024 * 1024;
+  static constexpr int TMEM_COLS = 2 * BX < 32 ? 32 : 2 * BX;        // two S tiles (power of two for BX in {64,128})
+  static constexpr int THREADS = 6 * 32;
+  static constexpr int BAR_A_FULL = 0;
+  static constexpr int BAR_X_FULL = 1;
+  static constexpr int BAR_X_EMPTY = BAR_X_FULL + STAGES;
+  static constexpr int BAR_N_FULL = BAR_X_EMPTY + STAGES;
+  static constexpr int BAR_N_EMPTY = BAR_N_FULL + STAGES;
+  static constexpr int BAR_T_FULL = BAR_N_EMPTY + STAGES;   // [2]
+  static constexpr int BAR_T_EMPTY = BAR_T_FULL + 2;        // [2]
+  static constexpr int BAR_DRAIN = BAR_T_EMPTY + 2;
+  static constexpr int NUM_BARS = BAR_DRAIN + 1;
+  static constexpr int SMEM_BYTES = A_BYTES + STAGES * X_STAGE_BYTES + STAGES * N_STAGE_STRIDE + NUM_BARS * 8 + 16 + 1024;
+};
+
+template <class Cfg>
+struct SweepCtx {
+  uint8_t* sA;
+  uint8_t* sX;
+  uint8_t* sN;
+  uint64_t* bars;
+  volatile int* abort_flag;
+  uint32_t tmem_base;
+  int a0;      // first stationary row (key index for the column sums, query index for the row LSE)
+  int bh, b, h;
+  int blk_lo, blk_hi;   // streamed blocks [blk_lo, blk_hi)
+};
+
+// ------------------------------- TMA producer -------------------------------
+template <class Cfg>
+__device__ __forceinline__ void sweep_producer(const SweepCtx<Cfg>& c, const SweepParams& p, const CUtensorMap* tm_a,
+                                               const CUtensorMap* tm_x, const CUtensorMap* tm_n) {
+  constexpr int ST = Cfg::STAGES, BX = Cfg::BX;
+  mbar_expect_tx(&c.bars[Cfg::BAR_A_FULL], Cfg::A_BYTES);
+#pragma unroll
+  for (int ks = 0; ks < 2; ++ks)
+    tma_load_4d(c.sA + ks * (Cfg::BM * 128), tm_a, &c.bars[Cfg::BAR_A_FULL], ks * 64, c.h, c.a0, c.b);
+  bool ok = true;
+  int n_issued = 0;
+  for (int blk = c.blk_lo; blk < c.blk_hi; ++blk) {
+    const int n = blk - c.blk_lo, st = n % ST, use = n / ST;
+    if (use > 0 && !mbar_wait(&c.bars[Cfg::BAR_X_EMPTY + st], (use - 1) & 1, c.abort_flag, WAIT_X_EMPTY)) {
+      ok = false;
+      break;
+    }
+    mbar_expect_tx(&c.bars[Cfg::BAR_X_FULL + st], Cfg::X_STAGE_BYTES);
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks)
+      tma_load_4d(c.sX + st * Cfg::X_STAGE_BYTES + ks * (BX * 128), tm_x, &c.bars[Cfg::BAR_X_FULL + st], ks * 64, c.h,
+                  blk * BX, c.b);
+    if constexpr (Cfg::N_STAGE_BYTES > 0) {
+      if (use > 0 && !mbar_wait(&c.bars[Cfg::BAR_N_EMPTY + st], (use - 1) & 1, c.abort_flag, WAIT_N_EMPTY)) {
+        ok = false;
+        n_issued = n;  // X(n) issued, N(n) not
+        break;
+      }
+      uint8_t* dst = c.sN + st * Cfg::N_STAGE_STRIDE;
+      mbar_expect_tx(&c.bars[Cfg::BAR_N_FULL + st], Cfg::N_STAGE_BYTES);
+      if constexpr (Cfg::NOISE) {
+        // exp_rand viewed as a [B*H*q_len, kv_len] fp32 matrix; panels of 32 columns
+        if constexpr (Cfg::MODE == SWEEP_KF_COLSUM) {
+          // rows = queries of the streamed block, columns = the 128 stationary keys
+#pragma unroll
+          for (int pn = 0; pn < 4; ++pn)
+            tma_load_2d(dst + pn * (BX * 128), tm_n, &c.bars[Cfg::BAR_N_FULL + st], c.a0 + pn * 32,
+                        c.bh * p.q_len + blk * BX);
+        } else {
+          // rows = the 128 stationary queries, columns = keys of the streamed block
+#pragma unroll
+          for (int pn = 0; pn < BX / 32; ++pn)
+            tma_load_2d(dst + pn * (128 * 128), tm_n, &c.bars[Cfg::BAR_N_FULL + st], blk * BX + pn * 32,
+                        c.bh * p.q_len + c.a0);
+        }
+      }
+      if constexpr (Cfg::LSE_IN) {
+        // 1-D bulk copy of the BX row normalisers of this query block (lse rows are padded to 128)
+        const float* src = p.lse + (int64_t)c.bh * p.lse_stride + blk * BX;
+        asm volatile(
+            "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+            ::"r"(smem_u32(dst + Cfg::NOISE_BYTES)), "l"(src), "r"((uint32_t)Cfg::LSE_BYTES),
+              "r"(smem_u32(&c.bars[Cfg::BAR_N_FULL + st]))
+            : "memory");
+      }
+    }
+    n_issued = n + 1;
+  }
+  if (!ok || *c.abort_flag != 0) {
+    // abort path: let our own bulk copies land before the CTA exits (bounded, 20 ms)
+    const uint64_t t0 = global_timer_ns();
+    while (!mbar_try_wait(&c.bars[Cfg::BAR_A_FULL], 0) && global_timer_ns() - t0 < 20000000ull) {
+    }
+    for (int st = 0; st < ST; ++st) {
+      const int u = (n_issued - 1 - st) >= 0 ? (n_issued - 1 - st) / ST : -1;
+      while (u >= 0 && !mbar_try_wait(&c.bars[Cfg::BAR_X_FULL + st], u & 1) && global_timer_ns() - t0 < 20000000ull) {
+      }
+      if constexpr (Cfg::N_STAGE_BYTES > 0) {
+        while (u >= 0 && !mbar_try_wait(&c.bars[Cfg::BAR_N_FULL + st], u & 1) &&
+               global_timer_ns() - t0 < 20000000ull) {
+        }
+      }
+    }
+  }
+}
+
+// -------------------------------- MMA issuer --------------------------------
+template <class Cfg, bool BF16>
+__device__ __forceinline__ void sweep_mma(const SweepCtx<Cfg>& c) {
+  constexpr int ST = Cfg::STAGES, BX = Cfg::BX;
+  constexpr uint32_t IDESC = make_idesc(BF16, 128, BX, false, false);
+  const uint32_t a_addr = smem_u32(c.sA), x_addr = smem_u32(c.sX);
+  bool ok = mbar_wait(&c.bars[Cfg::BAR_A_FULL], 0, c.abort_flag, WAIT_Q_FULL);
+  for (int blk = c.blk_lo; blk < c.blk_hi && ok; ++blk) {
+    const int n = blk - c.blk_lo, st = n % ST, tb = n & 1, tuse = n >> 1;
+    if (tuse > 0) ok = mbar_wait(&c.bars[Cfg::BAR_T_EMPTY + tb], (tuse - 1) & 1, c.abort_flag, WAIT_T_EMPTY);
+    ok = ok && mbar_wait(&c.bars[Cfg::BAR_X_FULL + st], (n / ST) & 1, c.abort_flag, WAIT_X_FULL);
+    if (!ok) break;
+    tc_fence_after();
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      const uint64_t a = make_smem_desc(a_addr + (kk / 4) * (128 * 128) + (kk % 4) * 32, 16, 1024);
+      const uint64_t bd = make_smem_desc(x_addr + st * Cfg::X_STAGE_BYTES + (kk / 4) * (BX * 128) + (kk % 4) * 32, 16, 1024);
+      umma_ss(c.tmem_base + tb * BX, a, bd, IDESC, kk > 0 ? 1u : 0u);
+    }
+    umma_commit(&c.bars[Cfg::BAR_T_FULL + tb]);
+    umma_commit(&c.bars[Cfg::BAR_X_EMPTY + st]);
+  }
+  umma_commit(&c.bars[Cfg::BAR_DRAIN]);
+  mbar_wait(&c.bars[Cfg::BAR_DRAIN], 0, c.abort_flag, WAIT_DRAIN);
+}
+
+// ------------------------- compute: per-key column sums -----------------------
+template <class Cfg, bool SOFTCAP, bool SQ>
+__device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, const SweepParams& p, int chunk) {
+  constexpr int ST = Cfg::STAGES, BX = Cfg::BX;
+  constexpr bool KF = Cfg::MODE == SWEEP_KF_COLSUM;
+  const int warp_q = (threadIdx.x >> 5) & 3, lane = threadIdx.x & 31;
+  const int key = c.a0 + warp_q * 32 + lane;
+  const uint32_t lane_addr = c.tmem_base + ((uint32_t)(warp_q * 32) << 16);
+  const float cmul = SOFTCAP ? 1.0f : p.scale_log2;
+  float acc0 = 0.f, acc1 = 0.f, sq0 = 0.f, sq1 = 0.f;
+
+  // queries visible to this key: [i_lo, i_hi]
+  int i_lo = p.causal ? key - p.delta : 0;
+  int i_hi = (p.causal && p.window > 0) ? min(p.q_len - 1, key + p.window - 1 - p.delta) : p.q_len - 1;
+  if (key >= p.kv_len) {
+    i_lo = 1 << 28;
+    i_hi = -1;
+  }
+
+  for (int blk = c.blk_lo; blk < c.blk_hi; ++blk) {
+    const int n = blk - c.blk_lo, st = n % ST, tb = n & 1;
+    if (!mbar_wait(&c.bars[Cfg::BAR_T_FULL + tb], (n >> 1) & 1, c.abort_flag, WAIT_T_FULL)) return;
+    if (!mbar_wait(&c.bars[Cfg::BAR_N_FULL + st], (n / ST) & 1, c.abort_flag, WAIT_N_FULL)) return;
+    tc_fence_after();
+    const uint8_t* nst = c.sN + st * Cfg::N_STAGE_STRIDE;
+    const float* lse_s = reinterpret_cast<const float*>(nst + Cfg::NOISE_BYTES);
+    const float* noise_col = reinterpret_cast<const float*>(nst + warp_q * (BX * 128)) + lane;  // + i * 32
+    const int i0 = blk * BX;
+    const int lo_c = i_lo - i0, hi_c = i_hi - i0;
+    // does any (key, query) pair of this block need masking?
+    const bool need_mask = (p.causal && (c.a0 + 127 - p.delta > i0)) || (i0 + BX > p.q_len) ||
+                           (c.a0 + 128 > p.kv_len) ||
+                           (p.causal && p.window > 0 && (c.a0 + p.window - 1 - p.delta < i0 + BX - 1));
+#pragma unroll
+    for (int ch = 0; ch < BX / 32; ++ch) {
+      uint32_t sr[32];
+      tmem_ld32(lane_addr + tb * BX + ch * 32, sr);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        const float4 L = *reinterpret_cast<const float4*>(lse_s + ch * 32 + i);
+        const float Lv[4] = {L.x, L.y, L.z, L.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          float s = __uint_as_float(sr[i + u]);
+          if constexpr (SOFTCAP) s = tanh_approx(s * p.cap_in) * p.cap_out;
+          float e;
+          if constexpr (KF) {
+            const float er = noise_col[(ch * 32 + i + u) * 32];
+            e = fmaf(fmaf(s, cmul, -lg2_approx(er)), p.inv_tau, -Lv[u]);
+          } else {
+            e = fmaf(s, cmul, -Lv[u]);
+          }
+          float pr = ex2_approx(e);
+          if (need_mask) {
+            const int col = ch * 32 + i + u;
+            if (col < lo_c || col > hi_c) pr = 0.f;
+          }
+          if (u & 1) {
+            acc1 += pr;
+            if constexpr (SQ) sq1 = fmaf(pr, pr, sq1);
+          } else {
+            acc0 += pr;
+            if constexpr (SQ) sq0 = fmaf(pr, pr, sq0);
+          }
+        }
+      }
+    }
+    // this TMEM buffer and this auxiliary stage may be refilled
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) {
+      mbar_arrive(&c.bars[Cfg::BAR_T_EMPTY + tb]);
+      mbar_arrive(&c.bars[Cfg::BAR_N_EMPTY + st]);
+    }
+  }
+  const int64_t off = ((int64_t)c.bh * p.n_chunks + chunk) * p.kv_pad + key;
+  p.partial[off] = acc0 + acc1;
+  if constexpr (SQ) p.partial_sq[off] = sq0 + sq1;
+}
+
+// --------------------- compute: per-query log-sum-exp of z --------------------
+template <class Cfg>
+__device__ __forceinline__ void sweep_compute_rowlse(const SweepCtx<Cfg>& c, const SweepParams& p) {
+  constexpr int ST = Cfg::STAGES, BX = Cfg::BX;
+  const int warp_q = (threadIdx.x >> 5) & 3, lane = threadIdx.x & 31;
+  const int r_local = warp_q * 32 + lane;
+  const int row = c.a0 + r_local;
+  const uint32_t lane_addr = c.tmem_base + ((uint32_t)(warp_q * 32) << 16);
+  const float cz = p.scale_log2 * p.inv_tau;
+  float m = -1.0e30f, l = 0.f;
+  const int hi_key = p.causal ? min(row + p.delta, p.kv_len - 1) : p.kv_len - 1;
+
+  for (int blk = c.blk_lo; blk < c.blk_hi; ++blk) {
+    const int n = blk - c.blk_lo, st = n % ST, tb = n & 1;
+    if (!mbar_wait(&c.bars[Cfg::BAR_T_FULL + tb], (n >> 1) & 1, c.abort_flag, WAIT_T_FULL)) return;
+    if (!mbar_wait(&c.bars[Cfg::BAR_N_FULL + st], (n / ST) & 1, c.abort_flag, WAIT_N_FULL)) return;
+    tc_fence_after();
+    const uint8_t* nst = c.sN + st * Cfg::N_STAGE_STRIDE;
+    const int hi_c = hi_key - blk * BX;
+    float z[BX];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int ch = 0; ch < BX / 32; ++ch) {
+      uint32_t sr[32];
+      tmem_ld32(lane_addr + tb * BX + ch * 32, sr);
+      tmem_ld_wait();
+      const uint8_t* panel = nst + ch * (128 * 128) + r_local * 128;
+#pragma unroll
+      for (int q4 = 0; q4 < 8; ++q4) {
+        // 128-byte swizzle written by TMA: 16-byte chunk q4 of row r sits at chunk (q4 ^ (r & 7))
+        const float4 er = *reinterpret_cast<const float4*>(panel + ((q4 ^ (r_local & 7)) << 4));
+        const float ev[4] = {er.x, er.y, er.z, er.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int col = ch * 32 + q4 * 4 + u;
+          float v = fmaf(__uint_as_float(sr[q4 * 4 + u]), cz, -lg2_approx(ev[u]) * p.inv_tau);
+          if (col > hi_c) v = -INFINITY;
+          z[col] = v;
+          mx = fmaxf(mx, v);
+        }
+      }
+    }
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) {
+      mbar_arrive(&c.bars[Cfg::BAR_T_EMPTY + tb]);
+      mbar_arrive(&c.bars[Cfg::BAR_N_EMPTY + st]);
+    }
+    const float m_new = fmaxf(m, mx);
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < BX; i += 2) {
+      s0 += ex2_approx(z[i] - m_new);
+      s1 += ex2_approx(z[i + 1] - m_new);
+    }
+    l = l * ex2_approx(m - m_new) + (s0 + s1);
+    m = m_new;
+  }
+  if (row < p.q_len) p.lse_out[(int64_t)c.bh * p.lse_stride + row] = m + log2f(l);
+}
+
+// ----------------------------------- kernel ----------------------------------
+template <int MODE, int BX, int STAGES, bool BF16, bool SOFTCAP, bool SQ>
+__global__ void __launch_bounds__(192, 1)
+attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_x,
+                  const __grid_constant__ CUtensorMap tm_n, const SweepParams p) {
+  using Cfg = SweepCfg<MODE, BX, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  // A launch that follows an expired wait on this device drains immediately (the status word stays
+  // set until the host reads it), so that one stuck kernel cannot stall a whole queue of launches.
+  __shared__ int s_skip;
+  if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(&g_device_status);
+  __syncthreads();
+  if (s_skip != 0) return;
+
+  SweepCtx<Cfg> c;
+  c.sA = smem;
+  c.sX = c.sA + Cfg::A_BYTES;
+  c.sN = c.sX + STAGES * Cfg::X_STAGE_BYTES;
+  c.bars = reinterpret_cast<uint64_t*>(c.sN + STAGES * Cfg::N_STAGE_STRIDE);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(c.bars + Cfg::NUM_BARS);
+  c.abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chunk = blockIdx.x;
+  c.a0 = blockIdx.y * 128;
+  c.bh = blockIdx.z;
+  c.b = c.bh / p.heads;
+  c.h = c.bh - c.b * p.heads;
+  if constexpr (MODE == SWEEP_KF_ROWLSE) {
+    const int r_last = min(c.a0 + 127, p.q_len - 1);
+    c.blk_lo = 0;
+    c.blk_hi = (p.causal ? min(p.kv_len - 1, r_last + p.delta) : p.kv_len - 1) / BX + 1;
+  } else {
+    const int i_first = p.causal ? max(0, c.a0 - p.delta) : 0;
+    const int i_last = (p.causal && p.window > 0) ? min(p.q_len - 1, c.a0 + 127 + p.window - 1 - p.delta) : p.q_len - 1;
+    const int lo = i_first / BX, hi = i_last / BX + 1;
+    c.blk_lo = max(lo, chunk * p.chunk_blocks);
+    c.blk_hi = min(hi, (chunk + 1) * p.chunk_blocks);
+    if (c.blk_hi < c.blk_lo) c.blk_hi = c.blk_lo;
+  }
+  if (c.blk_hi == c.blk_lo) {
+    // nothing visible in this chunk: its partial vector is all zeros
+    if constexpr (MODE != SWEEP_KF_ROWLSE) {
+      if (threadIdx.x < 128) {
+        const int64_t off = ((int64_t)c.bh * p.n_chunks + chunk) * p.kv_pad + c.a0 + threadIdx.x;
+        p.partial[off] = 0.f;
+        if constexpr (SQ) p.partial_sq[off] = 0.f;
+      }
+    }
+    return;
+  }
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int i = 0; i < Cfg::NUM_BARS; ++i) {
+      const bool warp_count = (i >= Cfg::BAR_N_EMPTY && i < Cfg::BAR_N_EMPTY + STAGES) ||
+                              (i >= Cfg::BAR_T_EMPTY && i < Cfg::BAR_T_EMPTY + 2);
+      mbar_init(&c.bars[i], warp_count ? 4u : 1u);
+    }
+    *c.abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_x);
+    if constexpr (Cfg::NOISE) tma_prefetch_desc(&tm_n);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  c.tmem_base = *tmem_slot;
+
+  if (warp < 4) {
+    if constexpr (MODE == SWEEP_KF_ROWLSE)
+      sweep_compute_rowlse<Cfg>(c, p);
+    else
+      sweep_compute_colsum<Cfg, SOFTCAP, SQ>(c, p, chunk);
+  } else if (warp == 4) {
+    if (lane == 0) sweep_producer<Cfg>(c, p, &tm_a, &tm_x, &tm_n);
+  } else {
+    if (lane == 0) sweep_mma<Cfg, BF16>(c);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(c.tmem_base, Cfg::TMEM_COLS);
+}
+
+// Adds the per-chunk partial vectors in chunk order: out[bh][j] = sum_c partial[bh][c][j].
+__global__ void __launch_bounds__(256)
+score_reduce_kernel(float* __restrict__ out, float* __restrict__ out_sq, const float* __restrict__ partial,
+                    const float* __restrict__ partial_sq, int kv_len, int kv_pad, int n_chunks) {
+  const int bh = blockIdx.y;
+  const int j = blockIdx.x * 256 + threadIdx.x;
+  if (j >= kv_len) return;
+  const float* src = partial + (int64_t)bh * n_chunks * kv_pad + j;
+  float a = 0.f;
+  for (int cidx = 0; cidx < n_chunks; ++cidx) a += src[(int64_t)cidx * kv_pad];
+  out[(int64_t)bh * kv_len + j] = a;
+  if (out_sq != nullptr) {
+    const float* src2 = partial_sq + (int64_t)bh * n_chunks * kv_pad + j;
+    float a2 = 0.f;
+    for (int cidx = 0; cidx < n_chunks; ++cidx) a2 += src2[(int64_t)cidx * kv_pad];
+    out_sq[(int64_t)bh * kv_len + j] = a2;
+  }
+}
+
+// --------------------------------- host side ---------------------------------
+constexpr int kSweepChunkBlocks = 8;   // streamed blocks per CTA in the column-sum sweeps
+
+struct ScoreWorkspace {
+  int lse_stride, kv_pad, n_chunks_colsum, n_chunks_kf;
+  int64_t lse_off, lse2_off, partial_off, partial_sq_off, total;
+};
+
+inline ScoreWorkspace score_workspace_layout(int batch, int q_len, int kv_len, int heads) {
+  ScoreWorkspace w;
+  const int64_t bh = (int64_t)batch * heads;
+  w.lse_stride = (q_len + 127) / 128 * 128;
+  w.kv_pad = (kv_len + 127) / 128 * 128;
+  const int qblocks128 = (q_len + 127) / 128, qblocks64 = (q_len + 63) / 64;
+  w.n_chunks_colsum = (qblocks128 + kSweepChunkBlocks - 1) / kSweepChunkBlocks;
+  w.n_chunks_kf = (qblocks64 + kSweepChunkBlocks - 1) / kSweepChunkBlocks;
+  const int n_chunks = std::max(w.n_chunks_colsum, w.n_chunks_kf);
+  auto up = [](int64_t x) { return (x + 255) / 256 * 256; };
+  w.lse_off = 0;
+  w.lse2_off = up(bh * w.lse_stride * 4);
+  w.partial_off = w.lse2_off + up(bh * w.lse_stride * 4);
+  w.partial_sq_off = w.partial_off + up(bh * n_chunks * w.kv_pad * 4);
+  w.total = w.partial_sq_off + up(bh * n_chunks * w.kv_pad * 4);
+  return w;
+}
+
+inline int64_t score_workspace_bytes(int batch, int q_len, int kv_len, int heads) {
+  if (batch <= 0 || q_len <= 0 || kv_len <= 0 || heads <= 0) return 0;
+  return score_workspace_layout(batch, q_len, kv_len, heads).total;
+}
+
+template <int MODE, int BX, int STAGES, bool BF16, bool SOFTCAP, bool SQ>
+int launch_sweep(const CUtensorMap& ta, const CUtensorMap& tx, const CUtensorMap& tn, const SweepParams& p,
+                 int grid_x, int grid_y, cudaStream_t stream) {
+  using Cfg = SweepCfg<MODE, BX, STAGES>;
+  auto kern = attn_sweep_kernel<MODE, BX, STAGES, BF16, SOFTCAP, SQ>;
+  static thread_local int configured_dev = -1;
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (configured_dev != dev) {
+    B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    configured_dev = dev;
+  }
+  dim3 grid(grid_x, grid_y, p.batch * p.heads);
+  kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tx, tn, p);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+inline int score_common_checks(const void* q, const void* k, const void* v, void* out, void* workspace,
+                               int64_t workspace_bytes, int batch, int q_len, int kv_len, int heads, int head_dim,
+                               int dtype) {
+  if (!q || !k || !v || !out) return B200_ERR_BAD_ARGUMENT;
+  if (batch <= 0 || q_len <= 0 || kv_len <= 0 || heads <= 0) return B200_ERR_BAD_ARGUMENT;
+  if (dtype != B200_F16 && dtype != B200_BF16) return B200_ERR_BAD_DTYPE;
+  if (head_dim != 128) return B200_ERR_UNSUPPORTED;
+  if (kv_len < q_len) return B200_ERR_UNSUPPORTED;
+  if ((int64_t)batch * heads > 65535) return B200_ERR_UNSUPPORTED;
+  if (!workspace || workspace_bytes < score_workspace_bytes(batch, q_len, kv_len, heads)) return B200_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return B200_ERR_MISALIGNED;
+  return B200_OK;
+}
+
+inline int attn_score_impl(const void* q, const void* k, const void* v, void* out, float* score, float* score_sq,
+                           void* workspace, int64_t workspace_bytes, int batch, int q_len, int kv_len, int heads,
+                           int head_dim, int dtype, int causal, int window, float softcap, float scale,
+                           cudaStream_t stream) {
+  int rc = score_common_checks(q, k, v, out, workspace, workspace_bytes, batch, q_len, kv_len, heads, head_dim, dtype);
+  if (rc != B200_OK) return rc;
+  if (!score) return B200_ERR_BAD_ARGUMENT;
+  if (window > 0 && !causal) return B200_ERR_UNSUPPORTED;
+  const ScoreWorkspace w = score_workspace_layout(batch, q_len, kv_len, heads);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  float* lse = reinterpret_cast<float*>(ws + w.lse_off);
+
+  rc = attn_fwd_impl_lse_stride(q, k, v, out, lse, w.lse_stride, batch, q_len, kv_len, heads, heads, head_dim, dtype,
+                                causal, window, softcap, scale, stream);
+  if (rc != B200_OK) return rc;
+
+  const bool bf16 = dtype == B200_BF16;
+  CUtensorMap ta, tx, tn;
+  if ((rc = make_bshd_tensor_map(&ta, k, batch, kv_len, heads, head_dim, 128, bf16)) != B200_OK) return rc;
+  if ((rc = make_bshd_tensor_map(&tx, q, batch, q_len, heads, head_dim, 128, bf16)) != B200_OK) return rc;
+  tn = ta;  // unused
+
+  SweepParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.lse = lse;
+  p.partial = reinterpret_cast<float*>(ws + w.partial_off);
+  p.partial_sq = reinterpret_cast<float*>(ws + w.partial_sq_off);
+  p.batch = batch;
+  p.heads = heads;
+  p.q_len = q_len;
+  p.kv_len = kv_len;
+  p.delta = kv_len - q_len;
+  p.causal = causal ? 1 : 0;
+  p.window = window > 0 ? window : 0;
+  p.lse_stride = w.lse_stride;
+  p.kv_pad = w.kv_pad;
+  p.n_chunks = w.n_chunks_colsum;
+  p.chunk_blocks = kSweepChunkBlocks;
+  const float kLog2e = 1.4426950408889634f;
+  p.scale_log2 = scale * kLog2e;
+  p.cap_in = softcap > 0.f ? scale / softcap : 0.f;
+  p.cap_out = softcap * kLog2e;
+  p.inv_tau = 1.0f;
+  const bool cap = softcap > 0.f, sq = score_sq != nullptr;
+  const int gy = w.kv_pad / 128;
+
+#define B200_SWEEP0(BF, CAP, SQF) launch_sweep<SWEEP_COLSUM, 128, 2, BF, CAP, SQF>(ta, tx, tn, p, p.n_chunks, gy, stream)
+  if (bf16)
+    rc = cap ? (sq ? B200_SWEEP0(true, true, true) : B200_SWEEP0(true, true, false))
+             : (sq ? B200_SWEEP0(true, false, true) : B200_SWEEP0(true, false, false));
+  else
+    rc = cap ? (sq ? B200_SWEEP0(false, true, true) : B200_SWEEP0(false, true, false))
+             : (sq ? B200_SWEEP0(false, false, true) : B200_SWEEP0(false, false, false));
+#undef B200_SWEEP0
+  if (rc != B200_OK) return rc;
+
+  dim3 rgrid((kv_len + 255) / 256, batch * heads);
+  score_reduce_kernel<<<rgrid, 256, 0, stream>>>(score, score_sq, p.partial, p.partial_sq, kv_len, w.kv_pad,
+                                                 p.n_chunks);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+inline int attn_kf_impl(const void* q, const void* k, const void* v, const float* exp_rand, void* out,
+                        float* kf_score, void* workspace, int64_t workspace_bytes, int batch, int q_len, int kv_len,
+                        int heads, int head_dim, int dtype, int causal, float tau, float scale, cudaStream_t stream) {
+  int rc = score_common_checks(q, k, v, out, workspace, workspace_bytes, batch, q_len, kv_len, heads, head_dim, dtype);
+  if (rc != B200_OK) return rc;
+  if (!exp_rand || !kf_score || !(tau > 0.f)) return B200_ERR_BAD_ARGUMENT;
+  if (kv_len % 4 != 0 || !aligned16(exp_rand)) return B200_ERR_MISALIGNED;
+  if ((int64_t)batch * heads * q_len >= (1ll << 31)) return B200_ERR_UNSUPPORTED;
+  const ScoreWorkspace w = score_workspace_layout(batch, q_len, kv_len, heads);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  float* lse2 = reinterpret_cast<float*>(ws + w.lse2_off);
+
+  // attention output (its own LSE is not needed by the KeyFormer score)
+  rc = attn_fwd_impl_lse_stride(q, k, v, out, nullptr, 0, batch, q_len, kv_len, heads, heads, head_dim, dtype, causal,
+                                0, 0.f, scale, stream);
+  if (rc != B200_OK) return rc;
+
+  const bool bf16 = dtype == B200_BF16;
+  CUtensorMap tq128, tk64, tk128, tq64, tn_rows128, tn_rows64;
+  if ((rc = make_bshd_tensor_map(&tq128, q, batch, q_len, heads, head_dim, 128, bf16)) != B200_OK) return rc;
+  if ((rc = make_bshd_tensor_map(&tq64, q, batch, q_len, heads, head_dim, 64, bf16)) != B200_OK) return rc;
+  if ((rc = make_bshd_tensor_map(&tk128, k, batch, kv_len, heads, head_dim, 128, bf16)) != B200_OK) return rc;
+  if ((rc = make_bshd_tensor_map(&tk64, k, batch, kv_len, heads, head_dim, 64, bf16)) != B200_OK) return rc;
+  const int64_t rows = (int64_t)batch * heads * q_len;
+  if ((rc = make_f32_matrix_tensor_map(&tn_rows128, exp_rand, rows, kv_len, 128, 32, true)) != B200_OK) return rc;
+  if ((rc = make_f32_matrix_tensor_map(&tn_rows64, exp_rand, rows, kv_len, 64, 32, false)) != B200_OK) return rc;
+
+  SweepParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.lse = lse2;
+  p.lse_out = lse2;
+  p.partial = reinterpret_cast<float*>(ws + w.partial_off);
+  p.partial_sq = nullptr;
+  p.batch = batch;
+  p.heads = heads;
+  p.q_len = q_len;
+  p.kv_len = kv_len;
+  p.delta = kv_len - q_len;
+  p.causal = causal ? 1 : 0;
+  p.window = 0;
+  p.lse_stride = w.lse_stride;
+  p.kv_pad = w.kv_pad;
+  p.n_chunks = w.n_chunks_kf;
+  p.chunk_blocks = kSweepChunkBlocks;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.inv_tau = 1.0f / tau;
+
+  // sweep 1: Lz_i = log2 sum_j exp2(z_ij), one CTA per 128 queries
+  const int q_tiles = (q_len + 127) / 128;
+  rc = bf16 ? launch_sweep<SWEEP_KF_ROWLSE, 64, 3, true, false, false>(tq128, tk64, tn_rows128, p, 1, q_tiles, stream)
+            : launch_sweep<SWEEP_KF_ROWLSE, 64, 3, false, false, false>(tq128, tk64, tn_rows128, p, 1, q_tiles, stream);
+  if (rc != B200_OK) return rc;
+  // sweep 2: per-key sums of exp2(z_ij - Lz_i)
+  const int gy = w.kv_pad / 128;
+  rc = bf16 ? launch_sweep<SWEEP_KF_COLSUM, 64, 3, true, false, false>(tk128, tq64, tn_rows64, p, p.n_chunks, gy, stream)
+            : launch_sweep<SWEEP_KF_COLSUM, 64, 3, false, false, false>(tk128, tq64, tn_rows64, p, p.n_chunks, gy, stream);
+  if (rc != B200_OK) return rc;
+
+  dim3 rgrid((kv_len + 255) / 256, batch * heads);
+  score_reduce_kernel<<<rgrid, 256, 0, stream>>>(kf_score, nullptr, p.partial, nullptr, kv_len, w.kv_pad, p.n_chunks);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+}  // namespace b200

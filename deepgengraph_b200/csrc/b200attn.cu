@@ -1,0 +1,207 @@
+// C ABI of the library (declared in include/b200attn.h).  The whole library is this one
+// translation unit: the kernels live in the .cuh files included below.
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+#include "elementwise.cuh"
+#include "attn_fwd.cuh"
+#include "attn_sweep.cuh"
+
+namespace b200 {
+
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+int make_bshd_tensor_map(CUtensorMap* map, const void* base, int batch, int seq, int heads, int dim, int box_rows,
+                         bool bf16) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return B200_ERR_CUDA;
+  const cuuint64_t dims[4] = {(cuuint64_t)dim, (cuuint64_t)heads, (cuuint64_t)seq, (cuuint64_t)batch};
+  const cuuint64_t strides[3] = {(cuuint64_t)dim * 2, (cuuint64_t)heads * dim * 2,
+                                 (cuuint64_t)seq * heads * dim * 2};
+  const cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = (int)r;
+    return B200_ERR_CUDA;
+  }
+  return B200_OK;
+}
+
+int make_f32_matrix_tensor_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int box_rows,
+                               int box_cols, bool swizzle128) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return B200_ERR_CUDA;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)cols * 4};
+  const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = (int)r;
+    return B200_ERR_CUDA;
+  }
+  return B200_OK;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+const char* b200_status_string(int status) {
+  switch (status) {
+    case B200_OK: return "ok";
+    case B200_ERR_BAD_ARGUMENT: return "bad argument";
+    case B200_ERR_BAD_DTYPE: return "unsupported dtype";
+    case B200_ERR_MISALIGNED: return "misaligned pointer or stride";
+    case B200_ERR_UNSUPPORTED: return "unsupported shape";
+    case B200_ERR_WORKSPACE: return "workspace missing or too small";
+    case B200_ERR_CUDA: return "CUDA call failed";
+    case B200_ERR_DEVICE_TIMEOUT: return "device-side wait expired";
+    default: return "unknown status";
+  }
+}
+
+int b200_last_cuda_error(void) { return g_last_cuda_error; }
+
+int b200_abi_version(void) { return 1; }
+
+int b200_device_status(int* status_out) {
+  if (!status_out) return B200_ERR_BAD_ARGUMENT;
+  int word = 0;
+  B200_CUDA_TRY(cudaDeviceSynchronize());
+  B200_CUDA_TRY(cudaMemcpyFromSymbol(&word, g_device_status, sizeof(int)));
+  if (word != 0) {
+    const int zero = 0;
+    B200_CUDA_TRY(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
+  }
+  *status_out = word;
+  return word == 0 ? B200_OK : B200_ERR_DEVICE_TIMEOUT;
+}
+
+int b200_rms_norm(void* out, const void* input, const void* weight, float epsilon, int64_t num_tokens,
+                  int hidden_size, int dtype, void* stream) {
+  if (!out || !input || !weight || num_tokens < 0 || hidden_size <= 0) return B200_ERR_BAD_ARGUMENT;
+  if (num_tokens == 0) return B200_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  void* in = const_cast<void*>(input);
+  switch (dtype) {
+    case B200_F32: return launch_rms_norm<float, false>(out, in, nullptr, weight, epsilon, num_tokens, hidden_size, s);
+    case B200_F16: return launch_rms_norm<__half, false>(out, in, nullptr, weight, epsilon, num_tokens, hidden_size, s);
+    case B200_BF16:
+      return launch_rms_norm<__nv_bfloat16, false>(out, in, nullptr, weight, epsilon, num_tokens, hidden_size, s);
+    default: return B200_ERR_BAD_DTYPE;
+  }
+}
+
+int b200_fused_add_rms_norm(void* input, void* residual, const void* weight, float epsilon, int64_t num_tokens,
+                            int hidden_size, int dtype, void* stream) {
+  if (!input || !residual || !weight || num_tokens < 0 || hidden_size <= 0) return B200_ERR_BAD_ARGUMENT;
+  if (num_tokens == 0) return B200_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dtype) {
+    case B200_F32:
+      return launch_rms_norm<float, true>(nullptr, input, residual, weight, epsilon, num_tokens, hidden_size, s);
+    case B200_F16:
+      return launch_rms_norm<__half, true>(nullptr, input, residual, weight, epsilon, num_tokens, hidden_size, s);
+    case B200_BF16:
+      return launch_rms_norm<__nv_bfloat16, true>(nullptr, input, residual, weight, epsilon, num_tokens, hidden_size,
+                                                  s);
+    default: return B200_ERR_BAD_DTYPE;
+  }
+}
+
+int b200_silu_and_mul(void* out, const void* input, int64_t num_tokens, int d, int dtype, void* stream) {
+  if (!out || !input || num_tokens < 0 || d <= 0) return B200_ERR_BAD_ARGUMENT;
+  if (num_tokens == 0) return B200_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dtype) {
+    case B200_F32: return launch_act_and_mul<float, SiluOp>(out, input, num_tokens, d, s);
+    case B200_F16: return launch_act_and_mul<__half, SiluOp>(out, input, num_tokens, d, s);
+    case B200_BF16: return launch_act_and_mul<__nv_bfloat16, SiluOp>(out, input, num_tokens, d, s);
+    default: return B200_ERR_BAD_DTYPE;
+  }
+}
+
+int b200_gelu_tanh_and_mul(void* out, const void* input, int64_t num_tokens, int d, int dtype, void* stream) {
+  if (!out || !input || num_tokens < 0 || d <= 0) return B200_ERR_BAD_ARGUMENT;
+  if (num_tokens == 0) return B200_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dtype) {
+    case B200_F32: return launch_act_and_mul<float, GeluTanhOp>(out, input, num_tokens, d, s);
+    case B200_F16: return launch_act_and_mul<__half, GeluTanhOp>(out, input, num_tokens, d, s);
+    case B200_BF16: return launch_act_and_mul<__nv_bfloat16, GeluTanhOp>(out, input, num_tokens, d, s);
+    default: return B200_ERR_BAD_DTYPE;
+  }
+}
+
+int b200_rotary_embedding_online(const int32_t* positions, void* query, void* key, int64_t num_tokens, int heads,
+                                 int kv_heads, int head_dim, int64_t query_stride, int64_t key_stride,
+                                 float rope_theta, int dtype, void* stream) {
+  if (!positions || !query || !key || num_tokens < 0 || heads <= 0 || kv_heads <= 0) return B200_ERR_BAD_ARGUMENT;
+  if (query_stride < (int64_t)heads * head_dim || key_stride < (int64_t)kv_heads * head_dim)
+    return B200_ERR_BAD_ARGUMENT;
+  if (num_tokens == 0) return B200_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dtype) {
+    case B200_F32:
+      return launch_rotary<float>(positions, query, key, num_tokens, heads, kv_heads, head_dim, query_stride,
+                                  key_stride, rope_theta, s);
+    case B200_F16:
+      return launch_rotary<__half>(positions, query, key, num_tokens, heads, kv_heads, head_dim, query_stride,
+                                   key_stride, rope_theta, s);
+    case B200_BF16:
+      return launch_rotary<__nv_bfloat16>(positions, query, key, num_tokens, heads, kv_heads, head_dim, query_stride,
+                                          key_stride, rope_theta, s);
+    default: return B200_ERR_BAD_DTYPE;
+  }
+}
+
+int b200_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int batch, int q_len,
+                  int kv_len, int heads, int kv_heads, int head_dim, int dtype, int causal, int window,
+                  float softcap, float scale, void* stream) {
+  return attn_fwd_impl(q, k, v, out, lse, batch, q_len, kv_len, heads, kv_heads, head_dim, dtype, causal, window,
+                       softcap, scale, (cudaStream_t)stream);
+}
+
+int64_t b200_attn_score_workspace_bytes(int batch, int q_len, int kv_len, int heads) {
+  return score_workspace_bytes(batch, q_len, kv_len, heads);
+}
+
+int b200_attn_score(const void* q, const void* k, const void* v, void* out, float* score, float* score_sq,
+                    void* workspace, int64_t workspace_bytes, int batch, int q_len, int kv_len, int heads,
+                    int head_dim, int dtype, int causal, int window, float softcap, float scale, void* stream) {
+  return attn_score_impl(q, k, v, out, score, score_sq, workspace, workspace_bytes, batch, q_len, kv_len, heads,
+                         head_dim, dtype, causal, window, softcap, scale, (cudaStream_t)stream);
+}
+
+int b200_attn_kf_score(const void* q, const void* k, const void* v, const float* exp_rand, void* out,
+                       float* kf_score, void* workspace, int64_t workspace_bytes, int batch, int q_len, int kv_len,
+                       int heads, int head_dim, int dtype, int causal, float tau, float scale, void* stream) {
+  return attn_kf_impl(q, k, v, exp_rand, out, kf_score, workspace, workspace_bytes, batch, q_len, kv_len, heads,
+                      head_dim, dtype, causal, tau, scale, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,357 @@
+// Bandwidth kernels: RMSNorm, fused-add RMSNorm, SiLU/GELU-gate, online rotary embedding.
+// All of them are HBM-bound; they move 16 bytes per thread per access, keep a row in
+// registers between the reduction and the scaling (one read of the input instead of
+// the two passes of the reference kernels), and run as persistent grids sized to the
+// SM count.
+#pragma once
+
+#include "common.cuh"
+
+namespace b200 {
+
+// ---------------------------------------------------------------------------
+// 16-byte vector of elements of type T
+// ---------------------------------------------------------------------------
+template <typename T>
+struct Vec16 {
+  static constexpr int N = 16 / sizeof(T);
+  uint4 raw;
+};
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T x);
+template <>
+__device__ __forceinline__ float to_f32<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half x) { return __half2float(x); }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float x);
+template <>
+__device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+template <typename T>
+__device__ __forceinline__ void unpack16(const uint4& raw, float (&f)[16 / sizeof(T)]) {
+  const T* p = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < (int)(16 / sizeof(T)); ++i) f[i] = to_f32<T>(p[i]);
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack16(const float (&f)[16 / sizeof(T)]) {
+  uint4 raw;
+  T* p = reinterpret_cast<T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < (int)(16 / sizeof(T)); ++i) p[i] = from_f32<T>(f[i]);
+  return raw;
+}
+
+__device__ __forceinline__ uint4 ld_nc_16(const void* p) {  // streaming read, no L1 allocation
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 ld_16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ void st_16(void* p, const uint4& v) { *reinterpret_cast<uint4*>(p) = v; }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Sum over the whole block; every thread receives the result.  `red` holds 33 floats.
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  constexpr int WARPS = THREADS / 32;
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  __syncthreads();  // protects `red` against the previous use
+  if (lane == 0) red[wid] = v;
+  __syncthreads();
+  float t = (lane < WARPS) ? red[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm.  out = T(x * rsqrt(mean(x^2) + eps)) * w, the last product taken in T
+// exactly as the reference does (csrc/norm.cu:54).
+// One block per row at a time, the row kept in registers: MAXV 16-byte vectors
+// per thread.  FUSED_ADD: x = input + residual, residual <- T(x), and the second
+// phase re-reads the ROUNDED residual like csrc/norm.cu:80 (variance from the
+// unrounded sum, csrc/norm.cu:68-70).
+// ---------------------------------------------------------------------------
+template <typename T, int THREADS, int MAXV, bool FUSED_ADD>
+__global__ void __launch_bounds__(THREADS)
+rms_norm_rows_kernel(T* __restrict__ out, T* __restrict__ input, T* __restrict__ residual,
+                     const T* __restrict__ weight, float epsilon, int64_t num_tokens, int hidden) {
+  constexpr int VN = 16 / sizeof(T);
+  __shared__ float red[33];
+  const int nvec = hidden / VN;  // hidden % VN == 0 checked on the host
+  for (int64_t row = blockIdx.x; row < num_tokens; row += gridDim.x) {
+    T* in_row = input + row * hidden;
+    float x[MAXV][VN];
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      const int idx = threadIdx.x + v * THREADS;
+      if (idx < nvec) {
+        unpack16<T>(FUSED_ADD ? ld_16(in_row + (int64_t)idx * VN) : ld_nc_16(in_row + (int64_t)idx * VN), x[v]);
+        if constexpr (FUSED_ADD) {
+          float r[VN];
+          T* res_row = residual + row * hidden;
+          unpack16<T>(ld_16(res_row + (int64_t)idx * VN), r);
+#pragma unroll
+          for (int i = 0; i < VN; ++i) {
+            x[v][i] += r[i];
+            ss += x[v][i] * x[v][i];
+          }
+          const uint4 rounded = pack16<T>(x[v]);
+          st_16(res_row + (int64_t)idx * VN, rounded);
+          unpack16<T>(rounded, x[v]);  // phase two sees the rounded residual
+        } else {
+#pragma unroll
+          for (int i = 0; i < VN; ++i) ss += x[v][i] * x[v][i];
+        }
+      }
+    }
+    const float total = block_sum<THREADS>(ss, red);
+    const float inv = rsqrtf(total / (float)hidden + epsilon);
+    T* out_row = (FUSED_ADD ? input : out) + row * hidden;
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      const int idx = threadIdx.x + v * THREADS;
+      if (idx < nvec) {
+        float w[VN], y[VN];
+        unpack16<T>(ld_16(weight + (int64_t)idx * VN), w);
+#pragma unroll
+        for (int i = 0; i < VN; ++i) y[i] = to_f32<T>(from_f32<T>(x[v][i] * inv)) * w[i];
+        st_16(out_row + (int64_t)idx * VN, pack16<T>(y));
+      }
+    }
+  }
+}
+
+// Generic fallback (any hidden size, any alignment): two passes over the row like the
+// reference, scalar accesses.  Only used for shapes the vector kernel cannot take.
+template <typename T, bool FUSED_ADD>
+__global__ void __launch_bounds__(256)
+rms_norm_generic_kernel(T* __restrict__ out, T* __restrict__ input, T* __restrict__ residual,
+                        const T* __restrict__ weight, float epsilon, int64_t num_tokens, int hidden) {
+  __shared__ float red[33];
+  for (int64_t row = blockIdx.x; row < num_tokens; row += gridDim.x) {
+    T* in_row = input + row * hidden;
+    T* res_row = FUSED_ADD ? residual + row * hidden : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += 256) {
+      float x = to_f32<T>(in_row[i]);
+      if constexpr (FUSED_ADD) {
+        x += to_f32<T>(res_row[i]);
+        res_row[i] = from_f32<T>(x);
+      }
+      ss += x * x;
+    }
+    const float total = block_sum<256>(ss, red);
+    const float inv = rsqrtf(total / (float)hidden + epsilon);
+    T* out_row = (FUSED_ADD ? input : out) + row * hidden;
+    for (int i = threadIdx.x; i < hidden; i += 256) {
+      const float x = to_f32<T>(FUSED_ADD ? res_row[i] : in_row[i]);
+      out_row[i] = from_f32<T>(to_f32<T>(from_f32<T>(x * inv)) * to_f32<T>(weight[i]));
+    }
+  }
+}
+
+template <typename T, bool FUSED_ADD>
+int launch_rms_norm(void* out, void* input, void* residual, const void* weight, float eps, int64_t num_tokens,
+                    int hidden, cudaStream_t stream) {
+  constexpr int VN = 16 / sizeof(T);
+  const int sms = sm_count();
+  const bool vec_ok = (hidden % VN == 0) && aligned16(input) && aligned16(weight) &&
+                      (FUSED_ADD ? aligned16(residual) : aligned16(out));
+  const int nvec = hidden / VN;
+  T* o = (T*)out;
+  T* in = (T*)input;
+  T* res = (T*)residual;
+  const T* w = (const T*)weight;
+  if (vec_ok && nvec <= 256 * 4) {
+    // 8 resident blocks of 256 threads per SM keep ~28 KB of loads in flight per SM
+    const int grid = (int)std::min<int64_t>(num_tokens, (int64_t)sms * 8);
+    if (nvec <= 256)
+      rms_norm_rows_kernel<T, 256, 1, FUSED_ADD><<<grid, 256, 0, stream>>>(o, in, res, w, eps, num_tokens, hidden);
+    else if (nvec <= 512)
+      rms_norm_rows_kernel<T, 256, 2, FUSED_ADD><<<grid, 256, 0, stream>>>(o, in, res, w, eps, num_tokens, hidden);
+    else
+      rms_norm_rows_kernel<T, 256, 4, FUSED_ADD><<<grid, 256, 0, stream>>>(o, in, res, w, eps, num_tokens, hidden);
+  } else {
+    const int grid = (int)std::min<int64_t>(num_tokens, (int64_t)sms * 8);
+    rms_norm_generic_kernel<T, FUSED_ADD><<<grid, 256, 0, stream>>>(o, in, res, w, eps, num_tokens, hidden);
+  }
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Gated activations.  out[t, i] = T(act(x)) * y with x = in[t, i], y = in[t, d + i]
+// (csrc/activation.cu:6-22: the activation is rounded to T, the product taken in T).
+// ---------------------------------------------------------------------------
+struct SiluOp {
+  __device__ __forceinline__ float operator()(float x) const { return x / (1.0f + __expf(-x)); }
+};
+struct GeluTanhOp {
+  __device__ __forceinline__ float operator()(float x) const {
+    const float kAlpha = 0.7978845608028654f;  // sqrt(2/pi)
+    const float inner = kAlpha * (x + 0.044715f * x * x * x);
+    return 0.5f * x * (1.0f + tanhf(inner));
+  }
+};
+
+template <typename T, typename Op>
+__global__ void __launch_bounds__(256)
+act_and_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ in, int64_t num_tokens, int d) {
+  constexpr int VN = 16 / sizeof(T);
+  const int vec_per_row = d / VN;
+  const int64_t total = num_tokens * vec_per_row;
+  Op op;
+  for (int64_t g = (int64_t)blockIdx.x * 256 + threadIdx.x; g < total; g += (int64_t)gridDim.x * 256) {
+    const int64_t t = g / vec_per_row;
+    const int c = (int)(g - t * vec_per_row);
+    const T* xrow = in + t * 2 * (int64_t)d;
+    float x[VN], y[VN], r[VN];
+    unpack16<T>(ld_nc_16(xrow + (int64_t)c * VN), x);
+    unpack16<T>(ld_nc_16(xrow + d + (int64_t)c * VN), y);
+#pragma unroll
+    for (int i = 0; i < VN; ++i) r[i] = to_f32<T>(from_f32<T>(op(x[i]))) * y[i];
+    st_16(out + t * (int64_t)d + (int64_t)c * VN, pack16<T>(r));
+  }
+}
+
+template <typename T, typename Op>
+__global__ void __launch_bounds__(256)
+act_and_mul_generic_kernel(T* __restrict__ out, const T* __restrict__ in, int64_t num_tokens, int d) {
+  const int64_t total = num_tokens * d;
+  Op op;
+  for (int64_t g = (int64_t)blockIdx.x * 256 + threadIdx.x; g < total; g += (int64_t)gridDim.x * 256) {
+    const int64_t t = g / d;
+    const int i = (int)(g - t * d);
+    const float x = to_f32<T>(in[t * 2 * (int64_t)d + i]);
+    const float y = to_f32<T>(in[t * 2 * (int64_t)d + d + i]);
+    out[g] = from_f32<T>(to_f32<T>(from_f32<T>(op(x))) * y);
+  }
+}
+
+template <typename T, typename Op>
+int launch_act_and_mul(void* out, const void* in, int64_t num_tokens, int d, cudaStream_t stream) {
+  constexpr int VN = 16 / sizeof(T);
+  const int sms = sm_count();
+  const bool vec_ok = (d % VN == 0) && aligned16(out) && aligned16(in);
+  if (vec_ok) {
+    const int64_t total = num_tokens * (d / VN);
+    const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((total + 255) / 256, (int64_t)sms * 16));
+    act_and_mul_vec_kernel<T, Op><<<grid, 256, 0, stream>>>((T*)out, (const T*)in, num_tokens, d);
+  } else {
+    const int64_t total = num_tokens * d;
+    const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((total + 255) / 256, (int64_t)sms * 16));
+    act_and_mul_generic_kernel<T, Op><<<grid, 256, 0, stream>>>((T*)out, (const T*)in, num_tokens, d);
+  }
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Online rotary embedding (NeoX pairing: element i rotates with element i + D/2),
+// csrc/pos_encoding.cu:83-111.  One block per token (grid-stride); the D/2 angles
+// are evaluated once per token with accurate powf/sincosf (the reference is built
+// with --use_fast_math; positions of several thousand radians lose most of their
+// precision there), then every head is rotated with 16-byte accesses.
+// ---------------------------------------------------------------------------
+template <typename T, int HEAD_DIM>
+__global__ void __launch_bounds__(256)
+rotary_online_kernel(const int32_t* __restrict__ positions, T* __restrict__ query, T* __restrict__ key,
+                     int64_t num_tokens, int heads, int kv_heads, int64_t q_stride, int64_t k_stride,
+                     float theta, int vec_ok) {
+  constexpr int HALF = HEAD_DIM / 2;
+  constexpr int VN = 16 / sizeof(T);
+  __shared__ float s_cos[HALF];
+  __shared__ float s_sin[HALF];
+  for (int64_t tok = blockIdx.x; tok < num_tokens; tok += gridDim.x) {
+    const float pos = (float)positions[tok];
+    __syncthreads();
+    for (int i = threadIdx.x; i < HALF; i += 256) {
+      const float freq = pos / powf(theta, (float)(2 * i) / (float)HEAD_DIM);
+      sincosf(freq, &s_sin[i], &s_cos[i]);
+    }
+    __syncthreads();
+    if (vec_ok) {
+      constexpr int VPH = HALF / VN;  // vectors per half head
+      const int total = (heads + kv_heads) * VPH;
+      for (int g = threadIdx.x; g < total; g += 256) {
+        const int head = g / VPH;
+        const int c = (g - head * VPH) * VN;
+        T* base = (head < heads) ? query + tok * q_stride + (int64_t)head * HEAD_DIM
+                                 : key + tok * k_stride + (int64_t)(head - heads) * HEAD_DIM;
+        float x[VN], y[VN], ox[VN], oy[VN];
+        unpack16<T>(ld_16(base + c), x);
+        unpack16<T>(ld_16(base + HALF + c), y);
+#pragma unroll
+        for (int i = 0; i < VN; ++i) {
+          const float cs = s_cos[c + i], sn = s_sin[c + i];
+          ox[i] = x[i] * cs - y[i] * sn;
+          oy[i] = y[i] * cs + x[i] * sn;
+        }
+        st_16(base + c, pack16<T>(ox));
+        st_16(base + HALF + c, pack16<T>(oy));
+      }
+    } else {
+      const int total = (heads + kv_heads) * HALF;
+      for (int g = threadIdx.x; g < total; g += 256) {
+        const int head = g / HALF;
+        const int c = g - head * HALF;
+        T* base = (head < heads) ? query + tok * q_stride + (int64_t)head * HEAD_DIM
+                                 : key + tok * k_stride + (int64_t)(head - heads) * HEAD_DIM;
+        const float x = to_f32<T>(base[c]), y = to_f32<T>(base[HALF + c]);
+        const float cs = s_cos[c], sn = s_sin[c];
+        base[c] = from_f32<T>(x * cs - y * sn);
+        base[HALF + c] = from_f32<T>(y * cs + x * sn);
+      }
+    }
+  }
+}
+
+template <typename T>
+int launch_rotary(const int32_t* positions, void* query, void* key, int64_t num_tokens, int heads, int kv_heads,
+                  int head_dim, int64_t q_stride, int64_t k_stride, float theta, cudaStream_t stream) {
+  constexpr int VN = 16 / sizeof(T);
+  const int vec_ok = aligned16(query) && aligned16(key) && (q_stride % VN == 0) && (k_stride % VN == 0) &&
+                     ((head_dim / 2) % VN == 0);
+  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(num_tokens, (int64_t)sm_count() * 8));
+  T* q = (T*)query;
+  T* k = (T*)key;
+  switch (head_dim) {
+    case 64:
+      rotary_online_kernel<T, 64><<<grid, 256, 0, stream>>>(positions, q, k, num_tokens, heads, kv_heads, q_stride,
+                                                            k_stride, theta, vec_ok);
+      break;
+    case 128:
+      rotary_online_kernel<T, 128><<<grid, 256, 0, stream>>>(positions, q, k, num_tokens, heads, kv_heads, q_stride,
+                                                             k_stride, theta, vec_ok);
+      break;
+    case 256:
+      rotary_online_kernel<T, 256><<<grid, 256, 0, stream>>>(positions, q, k, num_tokens, heads, kv_heads, q_stride,
+                                                             k_stride, theta, vec_ok);
+      break;
+    default:
+      return B200_ERR_UNSUPPORTED;
+  }
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+}  // namespace b200

@@ -1,0 +1,143 @@
+/*
+ * b200attn.h -- C ABI of the B200 (sm_100a) fused attention core modules and
+ * their companion bandwidth ops.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (passed as void*, may be NULL for the legacy default stream), enqueues its
+ * kernels on that stream and returns without synchronising.  The return value
+ * is a b200_status code (0 = success); nothing throws and nothing allocates
+ * device memory: scratch buffers are sized by the *_workspace_bytes queries and
+ * supplied by the caller.
+ *
+ * Tensor layouts follow the reference project (DeepGenGroup/DeepGenGraph):
+ *   q            [batch, q_len,  heads,    head_dim]   ("BSHD", contiguous)
+ *   k, v         [batch, kv_len, kv_heads, head_dim]
+ *   out          [batch, q_len,  heads,    head_dim]
+ *   score vectors[batch, heads, kv_len]  float32
+ *   exp_rand     [batch, heads, q_len, kv_len] float32
+ */
+#ifndef B200ATTN_H_
+#define B200ATTN_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of the 16/32-bit tensors */
+enum b200_dtype { B200_F32 = 0, B200_F16 = 1, B200_BF16 = 2 };
+
+enum b200_status {
+  B200_OK = 0,
+  B200_ERR_BAD_ARGUMENT = 1,   /* null pointer, non-positive size, unsupported head_dim ... */
+  B200_ERR_BAD_DTYPE = 2,      /* dtype not supported by this entry point            */
+  B200_ERR_MISALIGNED = 3,     /* pointer or stride not aligned as the kernel needs   */
+  B200_ERR_UNSUPPORTED = 4,    /* shape outside what the kernels implement            */
+  B200_ERR_WORKSPACE = 5,      /* workspace missing or too small                      */
+  B200_ERR_CUDA = 6,           /* a CUDA runtime/driver call failed (see b200_last_cuda_error) */
+  B200_ERR_DEVICE_TIMEOUT = 7  /* a bounded device-side wait expired (see b200_device_status)  */
+};
+
+/* Human-readable name of a status code. */
+const char* b200_status_string(int status);
+/* cudaError_t of the most recent failing CUDA call made by this library on the calling thread. */
+int b200_last_cuda_error(void);
+/* Library ABI version (bumped when a signature changes). */
+int b200_abi_version(void);
+
+/*
+ * Reads (and clears) the device-side status word of the current device.
+ * Kernels with bounded waits (mbarrier spins) record a non-zero code there and
+ * exit cleanly instead of hanging; 0 means no wait ever expired.  This call
+ * synchronises the device.  *status_out receives the raw word:
+ * bits 0..7 = which wait expired, bits 8..31 = (blockIdx.x & 0xffffff).
+ */
+int b200_device_status(int* status_out);
+
+/* ------------------------------------------------------------------------- *
+ * Bandwidth ops.  Replace the reference's csrc/ natives
+ * (csrc/ffi.cpp:4-8, csrc/op.h:2-6).
+ * ------------------------------------------------------------------------- */
+
+/* out = T(x * rsqrt(mean(x^2) + eps)) * weight   -- replaces rms_norm, csrc/norm.cu:34-56,85-98 */
+int b200_rms_norm(void* out, const void* input, const void* weight, float epsilon,
+                  int64_t num_tokens, int hidden_size, int dtype, void* stream);
+
+/* residual = T(input + residual); input = rms_norm(residual) * weight, both in place
+ * -- replaces fused_add_rms_norm, csrc/norm.cu:59-83,100-113 */
+int b200_fused_add_rms_norm(void* input, void* residual, const void* weight, float epsilon,
+                            int64_t num_tokens, int hidden_size, int dtype, void* stream);
+
+/* out[t, i] = T(silu(in[t, i])) * in[t, d + i]   -- replaces silu_and_mul, csrc/activation.cu:6-34 */
+int b200_silu_and_mul(void* out, const void* input, int64_t num_tokens, int d, int dtype,
+                      void* stream);
+
+/* out[t, i] = T(gelu_tanh(in[t, i])) * in[t, d + i] -- GeGLU sibling of silu_and_mul (same
+ * contract as csrc/activation.cu:6-34 with the tanh-approximated GELU as the gate). */
+int b200_gelu_tanh_and_mul(void* out, const void* input, int64_t num_tokens, int d, int dtype,
+                           void* stream);
+
+/* In-place NeoX-style rotary embedding with on-the-fly frequencies
+ * -- replaces rotary_embedding_online, csrc/pos_encoding.cu:64-113,180-199.
+ * query [num_tokens, heads * head_dim] with row stride query_stride (elements),
+ * key   [num_tokens, kv_heads * head_dim] with row stride key_stride,
+ * positions int32 [num_tokens].  head_dim in {64, 128, 256}. */
+int b200_rotary_embedding_online(const int32_t* positions, void* query, void* key,
+                                 int64_t num_tokens, int heads, int kv_heads, int head_dim,
+                                 int64_t query_stride, int64_t key_stride, float rope_theta,
+                                 int dtype, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Fused attention core modules.  Replace the kernels that the reference's
+ * compiler generates for deepgengraph_exp/cases/kernels/{attn,gemma2,h2o,roco,kf}.py
+ * (emitter: 3rd/deepgengraph/lib/Translate/to_triton.cpp:480-638).
+ * ------------------------------------------------------------------------- */
+
+/*
+ * out = softmax(mask(softcap(q k^T * scale))) v
+ *   -- Attn.forward   deepgengraph_exp/cases/kernels/attn.py:18-34
+ *   -- Gemma2.forward deepgengraph_exp/cases/kernels/gemma2.py:19-38 (softcap > 0)
+ * causal != 0 : key j visible to query i iff j <= i + (kv_len - q_len)
+ * window  > 0 : additionally i + (kv_len - q_len) - j < window
+ * softcap > 0 : logits <- softcap * tanh(logits / softcap) after scaling, before masking
+ * heads % kv_heads == 0 (grouped-query attention); head_dim in {128, 256}; dtype f16 or bf16.
+ * lse (optional, may be NULL): float32 [batch, heads, q_len], receives
+ *   log2(sum_j exp(logit_ij)) (base-2 log-sum-exp of the scaled, capped, masked logits);
+ *   the score passes below consume it.
+ */
+int b200_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
+                  int batch, int q_len, int kv_len, int heads, int kv_heads, int head_dim,
+                  int dtype, int causal, int window, float softcap, float scale, void* stream);
+
+/* Bytes of scratch that b200_attn_score / b200_attn_kf_score need for these sizes. */
+int64_t b200_attn_score_workspace_bytes(int batch, int q_len, int kv_len, int heads);
+
+/*
+ * Attention output plus per-key column sums of the fp32 softmax probabilities:
+ *   score[b, h, j]    = sum_i p_ij          -- H2O.forward  kernels/h2o.py:35-38
+ *   score_sq[b, h, j] = sum_i p_ij^2        -- RoCo.forward kernels/roco.py:42-48 (optional, may be NULL)
+ * heads must equal kv_heads (the reference asserts group_size == 1, kernels/h2o.py:16).
+ * workspace: at least b200_attn_score_workspace_bytes(...) bytes, 256-byte aligned.
+ */
+int b200_attn_score(const void* q, const void* k, const void* v, void* out, float* score,
+                    float* score_sq, void* workspace, int64_t workspace_bytes, int batch,
+                    int q_len, int kv_len, int heads, int head_dim, int dtype, int causal,
+                    int window, float softcap, float scale, void* stream);
+
+/*
+ * KeyFormer: attention output plus
+ *   kf_score[b, h, j] = sum_i softmax_j((logit_ij - log(exp_rand_ij)) / tau)
+ *   -- KeyFormer.forward kernels/kf.py:19-42
+ * exp_rand: float32 [batch, heads, q_len, kv_len], strictly positive.
+ * kv_len must be a multiple of 4 (16-byte rows of exp_rand).
+ */
+int b200_attn_kf_score(const void* q, const void* k, const void* v, const float* exp_rand,
+                       void* out, float* kf_score, void* workspace, int64_t workspace_bytes,
+                       int batch, int q_len, int kv_len, int heads, int head_dim, int dtype,
+                       int causal, float tau, float scale, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200ATTN_H_ */
