@@ -1,0 +1,105 @@
+"""Batch x head sharding of the core modules over the GPUs of one node (one process per GPU).
+
+Every (batch, kv-head) pair -- with the `group` query heads that share it -- is an independent unit of
+work: attention rows never mix heads, and the per-key score vectors of a head only sum over that head's
+own queries.  So the path shards with NO data-path collective: rank r owns the contiguous unit range
+[r*U/N, (r+1)*U/N) of the flattened (batch, kv_head) index space and runs the single-GPU kernels on it.
+The only communication is optional and off the critical path: gathering the small fp32 score vectors
+([units, kv_len], ~1 MiB in total) so that every rank sees the scores of all heads (a KV-eviction policy
+needs them where the layer's cache lives).  That gather is one NCCL all-gather over NVLink/NVSwitch;
+attention outputs stay sharded.
+
+The reference is single-GPU (our_env.sh:35,52); this module has no counterpart there.
+"""
+from dataclasses import dataclass
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def unit_range(n_units: int, world: int, rank: int) -> Tuple[int, int]:
+  """Contiguous, balanced split: the first (n_units % world) ranks own one extra unit."""
+  if world <= 0 or not (0 <= rank < world):
+    raise ValueError(f"bad rank/world {rank}/{world}")
+  base, extra = divmod(n_units, world)
+  lo = rank * base + min(rank, extra)
+  return lo, lo + base + (1 if rank < extra else 0)
+
+
+@dataclass(frozen=True)
+class Piece:
+  """A rectangular piece of a rank's shard: kv heads [hk_lo, hk_hi) of batch element b."""
+  b: int
+  hk_lo: int
+  hk_hi: int
+
+  @property
+  def n_units(self):
+    return self.hk_hi - self.hk_lo
+
+
+def shard_pieces(batch: int, kv_heads: int, world: int, rank: int) -> List[Piece]:
+  """The rank's unit range cut at batch boundaries (units are numbered b * kv_heads + hk)."""
+  lo, hi = unit_range(batch * kv_heads, world, rank)
+  pieces = []
+  u = lo
+  while u < hi:
+    b, hk = divmod(u, kv_heads)
+    end = min(hi, (b + 1) * kv_heads)
+    pieces.append(Piece(b, hk, hk + (end - u)))
+    u = end
+  return pieces
+
+
+def slice_piece(q, k, v, piece: Piece, group: int, extra=None):
+  """Contiguous BSHD views-made-dense of one piece: q heads [hk_lo*group, hk_hi*group), kv heads [hk_lo, hk_hi).
+  `extra` (optional) is a [B, H, Sq, Skv] tensor sliced the same way (KeyFormer's exp_rand)."""
+  b, lo, hi = piece.b, piece.hk_lo, piece.hk_hi
+  qs = q[b:b + 1, :, lo * group:hi * group].contiguous()
+  ks = k[b:b + 1, :, lo:hi].contiguous()
+  vs = v[b:b + 1, :, lo:hi].contiguous()
+  if extra is None:
+    return qs, ks, vs
+  return qs, ks, vs, extra[b:b + 1, lo * group:hi * group].contiguous()
+
+
+def run_sharded(fn, q, k, v, world: int, rank: int, extra=None):
+  """Runs `fn(q_piece, k_piece, v_piece[, extra_piece])` on this rank's pieces of the full problem.
+  Returns a list of (piece, result) -- results stay on the device, sharded."""
+  group = q.size(2) // k.size(2)
+  out = []
+  for piece in shard_pieces(q.size(0), k.size(2), world, rank):
+    args = slice_piece(q, k, v, piece, group, extra)
+    out.append((piece, fn(*args)))
+  return out
+
+
+def gather_scores(local_scores: torch.Tensor, n_units_total: int, world: int, rank: int,
+                  group: Optional["dist.ProcessGroup"] = None) -> torch.Tensor:
+  """All-gathers per-unit score vectors.  local_scores: [units_local, kv_len] float32, rows in unit order.
+  Returns [n_units_total, kv_len] on every rank (unit u = b * heads + h).  Uneven splits are padded to the
+  largest shard for the collective and trimmed afterwards."""
+  lo, hi = unit_range(n_units_total, world, rank)
+  if local_scores.size(0) != hi - lo:
+    raise ValueError(f"rank {rank} owns {hi - lo} units but passed {local_scores.size(0)} score rows")
+  if world == 1:
+    return local_scores
+  kv_len = local_scores.size(1)
+  max_units = -(-n_units_total // world)
+  send = local_scores
+  if send.size(0) < max_units:
+    send = torch.cat([send, send.new_zeros(max_units - send.size(0), kv_len)], dim=0)
+  recv = send.new_empty(world * max_units, kv_len)
+  dist.all_gather_into_tensor(recv, send.contiguous(), group=group)
+  rows = []
+  for r in range(world):
+    rlo, rhi = unit_range(n_units_total, world, r)
+    rows.append(recv[r * max_units:r * max_units + (rhi - rlo)])
+  return torch.cat(rows, dim=0)
+
+
+def scores_from_pieces(results, index: int = 1) -> torch.Tensor:
+  """Stacks the score output `index` of run_sharded results into [units_local, kv_len] in unit order."""
+  rows = [res[index].reshape(-1, res[index].size(-1)) for _, res in results]
+  return torch.cat(rows, dim=0) if rows else torch.empty(0)

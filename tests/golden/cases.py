@@ -29,7 +29,7 @@ CASES = {
     "attn_s192": dict(model="attn", B=1, Sq=192, Skv=192, H=2, D=128),
     "attn_sq128_skv320": dict(model="attn", B=1, Sq=128, Skv=320, H=2, D=128),
     "attn_b2_s256": dict(model="attn", B=2, Sq=256, Skv=256, H=3, D=128),
-    "gemma2_s192": dict(model="gemma2", B=1, Sq=192, Skv=192, H=2, D=128, q_gain=24.0),
+    "gemma2_s192": dict(model="gemma2", B=1, Sq=192, Skv=192, H=2, D=128, q_gain=16.0),
     "h2o_s256": dict(model="h2o", B=1, Sq=256, Skv=256, H=2, D=128),
     "h2o_sq64_skv192": dict(model="h2o", B=1, Sq=64, Skv=192, H=2, D=128),
     "roco_s192": dict(model="roco", B=1, Sq=192, Skv=192, H=2, D=128),

@@ -1,0 +1,88 @@
+"""Host logic of the batch x head sharding: partition arithmetic, piece slicing, and the score gather on
+world_size-2 (and 3) gloo process groups on CPU."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from deepgengraph_b200 import sharding as sh
+
+
+def test_unit_ranges_partition_exactly():
+  for n in (1, 7, 8, 64, 128, 130):
+    for world in (1, 2, 3, 4, 8):
+      spans = [sh.unit_range(n, world, r) for r in range(world)]
+      assert spans[0][0] == 0 and spans[-1][1] == n
+      for (a, b), (c, d) in zip(spans, spans[1:]):
+        assert b == c
+      sizes = [b - a for a, b in spans]
+      assert max(sizes) - min(sizes) <= 1
+  with pytest.raises(ValueError):
+    sh.unit_range(8, 2, 2)
+
+
+def test_pieces_cover_every_unit_once():
+  for batch, kvh, world in ((4, 32, 8), (2, 32, 3), (1, 8, 8), (2, 8, 5), (3, 5, 4)):
+    seen = []
+    for r in range(world):
+      for p in sh.shard_pieces(batch, kvh, world, r):
+        assert 0 <= p.hk_lo < p.hk_hi <= kvh
+        seen += [p.b * kvh + h for h in range(p.hk_lo, p.hk_hi)]
+    assert seen == list(range(batch * kvh))
+
+
+def test_slice_piece_and_run_sharded_reassemble_the_full_problem():
+  B, S, H, Hk, D = 2, 16, 6, 3, 8
+  q = torch.arange(B * S * H * D, dtype=torch.float32).view(B, S, H, D)
+  k = torch.arange(B * S * Hk * D, dtype=torch.float32).view(B, S, Hk, D) + 0.5
+  v = -k
+  extra = torch.arange(B * H * S * S, dtype=torch.float32).view(B, H, S, S)
+  world = 4
+  out = torch.full_like(q, float("nan"))
+  ex = torch.full_like(extra, float("nan"))
+  for r in range(world):
+    for piece, (qs, ks, vs, es) in sh.run_sharded(lambda a, b, c, e: (a, b, c, e), q, k, v, world, r, extra=extra):
+      g = H // Hk
+      assert qs.is_contiguous() and ks.shape[2] * g == qs.shape[2]
+      assert torch.equal(vs, -ks)
+      out[piece.b, :, piece.hk_lo * g:piece.hk_hi * g] = qs[0]
+      ex[piece.b, piece.hk_lo * g:piece.hk_hi * g] = es[0]
+  assert torch.equal(out, q) and torch.equal(ex, extra)
+
+
+def _free_port():
+  s = socket.socket()
+  s.bind(("127.0.0.1", 0))
+  port = s.getsockname()[1]
+  s.close()
+  return port
+
+
+def _gather_worker(rank, world, port, n_units, kv_len, fail_rank):
+  os.environ["MASTER_ADDR"] = "127.0.0.1"
+  os.environ["MASTER_PORT"] = str(port)
+  dist.init_process_group("gloo", rank=rank, world_size=world)
+  try:
+    lo, hi = sh.unit_range(n_units, world, rank)
+    local = torch.stack([torch.full((kv_len,), float(u)) + torch.arange(kv_len) / 1000.0 for u in range(lo, hi)]) \
+        if hi > lo else torch.empty(0, kv_len)
+    full = sh.gather_scores(local, n_units, world, rank)
+    expect = torch.stack([torch.full((kv_len,), float(u)) + torch.arange(kv_len) / 1000.0 for u in range(n_units)])
+    assert torch.equal(full, expect), f"rank {rank}: gathered layout is wrong"
+    if rank == fail_rank:
+      # a rank that passes the wrong number of rows is caught on the host, before any collective
+      try:
+        sh.gather_scores(local[:-1], n_units, world, rank)
+        raise AssertionError("row-count mismatch was not detected")
+      except ValueError:
+        pass
+  finally:
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,n_units", [(2, 64), (2, 7), (3, 8)])
+def test_score_gather_on_gloo(world, n_units):
+  mp.spawn(_gather_worker, args=(world, _free_port(), n_units, 33, 0), nprocs=world, join=True)
