@@ -131,12 +131,17 @@ def cpu_reference_sample(budget_s, threads=None):
   t0 = time.perf_counter()
   rm.attention_ref(q, k, v, causal=True, head_chunk=1)
   t1 = time.perf_counter() - t0
-  heads = max(1, min(8, int(budget_s / max(t1, 1e-3))))
+  heads = max(1, min(16, int(budget_s / max(t1, 1e-3))))
   qh, kh, vh = (t.expand(1, S, heads, D).contiguous() for t in (q, k, v))
-  t0 = time.perf_counter()
-  rm.attention_ref(qh, kh, vh, causal=True, head_chunk=2)
-  dt = time.perf_counter() - t0
-  return causal_flops(1, heads, S, D) / dt / 1e12, cores, f"{heads} of {B * H} (batch, head) units of config2, fp32, {dt:.2f} s"
+  passes, t0 = 0, time.perf_counter()
+  while True:
+    rm.attention_ref(qh, kh, vh, causal=True, head_chunk=2)
+    passes += 1
+    dt = time.perf_counter() - t0
+    if dt >= budget_s or passes >= 64:
+      break
+  return (causal_flops(1, heads, S, D) * passes / dt / 1e12, cores,
+          f"{passes} pass(es) over {heads} of {B * H} (batch, head) units of config2, fp32, {dt:.1f} s")
 
 
 def run_reference_arm(args, rank, world):

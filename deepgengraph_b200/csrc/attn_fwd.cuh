@@ -44,7 +44,9 @@ struct FwdCfg {
   static constexpr int TMEM_COLS = TMEM_USED <= 32 ? 32 : TMEM_USED <= 64 ? 64 : TMEM_USED <= 128 ? 128
                                    : TMEM_USED <= 256 ? 256 : 512;
   static_assert(TMEM_USED <= 512, "TMEM budget exceeded");
-  static constexpr int THREADS = (NQ * 4 + 2) * 32;
+  // NQ = 2 pads the producer/MMA warps to a full warpgroup so that registers can be re-balanced per warpgroup
+  static constexpr int THREADS = NQ == 2 ? 384 : (NQ * 4 + 2) * 32;
+  static constexpr bool REBALANCE_REGS = NQ == 2;
   // barrier slots
   static constexpr int BAR_Q_FULL = 0;                       // [NQ]
   static constexpr int BAR_S_FULL = BAR_Q_FULL + NQ;         // [NQ]
@@ -157,7 +159,11 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<Cfg, BF16>& c) {
   constexpr int ST = Cfg::STAGES, D = Cfg::D, BN = Cfg::BN, BM = Cfg::BM, NQ = Cfg::NQ;
   constexpr uint32_t IDESC_S = make_idesc(BF16, BM, BN, false, false);
   constexpr uint32_t IDESC_PV = make_idesc(BF16, BM, D, false, true);
-  const uint32_t q_addr = smem_u32(c.sQ), k_addr = smem_u32(c.sK), v_addr = smem_u32(c.sV);
+  // descriptor halves: the upper word is constant, the lower word is (address >> 4) plus a compile-time step
+  constexpr uint32_t DESC_HI = smem_desc_hi(1024);
+  const uint32_t q_lo = smem_desc_lo(smem_u32(c.sQ), 16);
+  const uint32_t k_lo = smem_desc_lo(smem_u32(c.sK), 16);
+  const uint32_t v_lo = smem_desc_lo(smem_u32(c.sV), BN * 128);   // MN-major: LBO = bytes between 64-wide column blocks
   int k_ready = c.jmin - 1, v_ready = c.jmin - 1;  // last block whose K / V stage has been observed full
   bool ok = true;
 
@@ -171,11 +177,14 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<Cfg, BF16>& c) {
     if (!ok) return;
     tc_fence_after();
     const uint32_t d_tmem = c.tmem_base + t * BN;
+    const uint32_t a0 = q_lo + (uint32_t)(t * (Cfg::Q_TILE_BYTES >> 4));
+    const uint32_t b0 = k_lo + (uint32_t)(st * (Cfg::KV_STAGE_BYTES >> 4));
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
-      const uint64_t a = make_smem_desc(q_addr + t * Cfg::Q_TILE_BYTES + (kk / 4) * (BM * 128) + (kk % 4) * 32, 16, 1024);
-      const uint64_t bdesc = make_smem_desc(k_addr + st * Cfg::KV_STAGE_BYTES + (kk / 4) * (BN * 128) + (kk % 4) * 32, 16, 1024);
-      umma_ss(d_tmem, a, bdesc, IDESC_S, kk > 0 ? 1u : 0u);
+      const uint32_t a_off = (uint32_t)(((kk / 4) * (BM * 128) + (kk % 4) * 32) >> 4);
+      const uint32_t b_off = (uint32_t)(((kk / 4) * (BN * 128) + (kk % 4) * 32) >> 4);
+      umma_ss(d_tmem, desc_from_halves(a0 + a_off, DESC_HI), desc_from_halves(b0 + b_off, DESC_HI), IDESC_S,
+              kk > 0 ? 1u : 0u);
     }
     umma_commit(&c.bars[Cfg::BAR_S_FULL + t]);
   };
@@ -190,11 +199,13 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<Cfg, BF16>& c) {
     tc_fence_after();
     const uint32_t d_tmem = c.tmem_base + Cfg::O_BASE + t * D;
     const uint32_t a_tmem = c.tmem_base + t * BN;  // P: packed 16-bit pairs, 8 columns per 16 keys
+    const uint32_t b0 = v_lo + (uint32_t)(st * (Cfg::KV_STAGE_BYTES >> 4));
+    const uint32_t first = (j > c.rng[t].lo) ? 1u : 0u;
 #pragma unroll
     for (int kk = 0; kk < BN / 16; ++kk) {
-      // V stage: KSUB column blocks of [BN keys][64 dims]; MN-major B operand
-      const uint64_t bdesc = make_smem_desc(v_addr + st * Cfg::KV_STAGE_BYTES + kk * 2048, BN * 128, 1024);
-      umma_ts(d_tmem, a_tmem + kk * 8, bdesc, IDESC_PV, (j > c.rng[t].lo || kk > 0) ? 1u : 0u);
+      // V stage: KSUB column blocks of [BN keys][64 dims]; 16 keys = 2048 bytes further down
+      umma_ts(d_tmem, a_tmem + kk * 8, desc_from_halves(b0 + (uint32_t)(kk * (2048 >> 4)), DESC_HI), IDESC_PV,
+              kk > 0 ? 1u : first);
     }
     umma_commit(&c.bars[Cfg::BAR_O_FULL + t]);
   };
@@ -223,6 +234,99 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<Cfg, BF16>& c) {
 }
 
 // ------------------------------ softmax warpgroup ----------------------------
+// One block of the online softmax for one row (thread).  MASK selects the edge-block variant.
+template <class Cfg, bool BF16, bool SOFTCAP, bool MASK>
+__device__ __forceinline__ bool fwd_softmax_block(const FwdCtx<Cfg, BF16>& c, const FwdParams& p, uint32_t s_addr,
+                                                  uint32_t o_addr, uint64_t* o_full, uint64_t* p_full, int n,
+                                                  int lo_c, int hi_c, float cmul, float& m, float& l) {
+  constexpr int D = Cfg::D, BN = Cfg::BN;
+  const int lane = threadIdx.x & 31;
+  uint32_t sr[BN / 32][32];
+#pragma unroll
+  for (int ch = 0; ch < BN / 32; ++ch) tmem_ld32(s_addr + ch * 32, sr[ch]);
+  tmem_ld_wait();
+
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+  for (int ch = 0; ch < BN / 32; ++ch) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      float v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float s = __uint_as_float(sr[ch][i + u]);
+        if constexpr (SOFTCAP) s = tanh_approx(s * p.cap_in);   // cap_out is folded into cmul
+        if constexpr (MASK) {
+          const int col = ch * 32 + i + u;
+          if (col > hi_c || col < lo_c) s = -INFINITY;
+        }
+        if constexpr (SOFTCAP || MASK) sr[ch][i + u] = __float_as_uint(s);
+        v[u] = s;
+      }
+      mx0 = fmax3(mx0, v[0], v[1]);
+      mx1 = fmax3(mx1, v[2], v[3]);
+    }
+  }
+  const float m_blk = fmaxf(mx0, mx1) * cmul;  // -inf when the whole row is masked inside this block
+  float alpha = 1.0f;
+  bool rescale = false;
+  if (n == 0) {
+    m = fmaxf(m, m_blk);
+  } else if (m_blk - m > 8.0f) {
+    // Lazy rescale: the running reference only moves when the new maximum exceeds it by more than 2^8, so
+    // that exp2(x - m) stays <= 256 and the O accumulator is touched rarely.
+    alpha = ex2_approx(m - m_blk);
+    m = m_blk;
+    l *= alpha;
+    rescale = true;
+  }
+  if (n > 0 && __any_sync(0xffffffffu, rescale)) {
+    if (!mbar_wait(o_full, (n - 1) & 1, c.abort_flag, WAIT_O_FULL)) return false;
+    tc_fence_after();
+    const float2 a2 = make_float2(alpha, alpha);
+#pragma unroll
+    for (int ch = 0; ch < D / 16; ++ch) {
+      uint32_t o[16];
+      tmem_ld16(o_addr + ch * 16, o);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; i += 2) {
+        const float2 r = fmul2(make_float2(__uint_as_float(o[i]), __uint_as_float(o[i + 1])), a2);
+        o[i] = __float_as_uint(r.x);
+        o[i + 1] = __float_as_uint(r.y);
+      }
+      tmem_st16(o_addr + ch * 16, o);
+    }
+  }
+  // P = exp2(x - m), packed to the 16-bit input type, written over the first BN/2 columns of S
+  const float2 c2 = make_float2(cmul, cmul), nm2 = make_float2(-m, -m);
+  float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+#pragma unroll
+  for (int ch = 0; ch < BN / 32; ++ch) {
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      float2 x0 = ffma2(make_float2(__uint_as_float(sr[ch][i + 0]), __uint_as_float(sr[ch][i + 1])), c2, nm2);
+      float2 x1 = ffma2(make_float2(__uint_as_float(sr[ch][i + 2]), __uint_as_float(sr[ch][i + 3])), c2, nm2);
+      x0.x = ex2_approx(x0.x);
+      x0.y = ex2_approx(x0.y);
+      x1.x = ex2_approx(x1.x);
+      x1.y = ex2_approx(x1.y);
+      acc0 = fadd2(acc0, x0);
+      acc1 = fadd2(acc1, x1);
+      pk[i / 2] = pack2<BF16>(x0.x, x0.y);
+      pk[i / 2 + 1] = pack2<BF16>(x1.x, x1.y);
+    }
+    tmem_st16(s_addr + ch * 16, pk);
+  }
+  l += (acc0.x + acc0.y) + (acc1.x + acc1.y);
+  tmem_st_wait();
+  tc_fence_before();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(p_full);
+  return true;
+}
+
 template <class Cfg, bool BF16, bool SOFTCAP>
 __device__ __forceinline__ void fwd_softmax(const FwdCtx<Cfg, BF16>& c, const FwdParams& p, int t) {
   constexpr int D = Cfg::D, BN = Cfg::BN;
@@ -238,94 +342,28 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<Cfg, BF16>& c, const Fw
   uint64_t* p_full = &c.bars[Cfg::BAR_P_FULL + t];
   uint64_t* o_full = &c.bars[Cfg::BAR_O_FULL + t];
 
-  const float cmul = SOFTCAP ? 1.0f : p.scale_log2;
+  const float cmul = SOFTCAP ? p.cap_out : p.scale_log2;
   float m = -1.0e30f;  // running reference maximum (base-2 units); finite so that fully masked blocks stay NaN-free
   float l = 0.f;
+  // visible keys of this row: [lo_key, hi_key]
+  const int hi_key = p.causal ? min(row + p.delta, p.kv_len - 1) : p.kv_len - 1;
+  const int lo_key = (p.causal && p.window > 0) ? (row + p.delta - p.window + 1) : -(1 << 28);
+  const int hi_first = p.causal ? min(r_tile + p.delta, p.kv_len - 1) : p.kv_len - 1;          // first row of the tile
+  const int lo_last = (p.causal && p.window > 0) ? (r_tile + 127 + p.delta - p.window + 1) : -(1 << 28);  // last row
 
   for (int j = rng.lo; j < rng.hi; ++j) {
     const int n = j - rng.lo;
     if (!mbar_wait(s_full, n & 1, c.abort_flag, WAIT_S_FULL)) return;
     tc_fence_after();
-    uint32_t sr[BN / 32][32];
-#pragma unroll
-    for (int ch = 0; ch < BN / 32; ++ch) tmem_ld32(s_addr + ch * 32, sr[ch]);
-    tmem_ld_wait();
-
-    // visible columns of this row inside the block: [lo_c, hi_c]
-    const int hi_key = p.causal ? min(row + p.delta, p.kv_len - 1) : p.kv_len - 1;
-    const int hi_c = hi_key - j * BN;
-    const int lo_c = (p.causal && p.window > 0) ? (row + p.delta - p.window + 1 - j * BN) : -(1 << 28);
-    const int hi_first = (p.causal ? min(r_tile + p.delta, p.kv_len - 1) : p.kv_len - 1) - j * BN;
-    const bool need_mask = (hi_first < BN - 1) ||
-                           (p.causal && p.window > 0 && (r_tile + 127 + p.delta - p.window + 1 - j * BN) > 0);
-
-    float mx = -INFINITY;
-#pragma unroll
-    for (int ch = 0; ch < BN / 32; ++ch) {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        float s = __uint_as_float(sr[ch][i]);
-        if constexpr (SOFTCAP) s = tanh_approx(s * p.cap_in) * p.cap_out;
-        if (need_mask) {
-          const int col = ch * 32 + i;
-          if (col > hi_c || col < lo_c) s = -INFINITY;
-        }
-        sr[ch][i] = __float_as_uint(s);
-        mx = fmaxf(mx, s);
-      }
-    }
-    const float m_blk = mx * cmul;  // -inf when the whole row is masked inside this block
-    float alpha = 1.0f;
-    bool rescale = false;
-    if (n == 0) {
-      m = fmaxf(m, m_blk);
-    } else if (m_blk - m > 8.0f) {
-      // Lazy rescale: the running reference only moves when the new maximum exceeds it by more
-      // than 2^8, so that exp2(x - m) stays <= 256 and O is touched rarely.
-      alpha = ex2_approx(m - m_blk);
-      m = m_blk;
-      l *= alpha;
-      rescale = true;
-    }
-    if (n > 0 && __any_sync(0xffffffffu, rescale)) {
-      if (!mbar_wait(o_full, (n - 1) & 1, c.abort_flag, WAIT_O_FULL)) return;
-      tc_fence_after();
-#pragma unroll
-      for (int ch = 0; ch < D / 32; ++ch) {
-        uint32_t o[32];
-        tmem_ld32(o_addr + ch * 32, o);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-        tmem_st32(o_addr + ch * 32, o);
-      }
-    }
-    // P = exp2(x - m), packed to the 16-bit input type, written over the first BN/2 columns of S
-    const float neg_m = -m;
-    float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-#pragma unroll
-    for (int ch = 0; ch < BN / 64; ++ch) {
-      uint32_t pk[32];
-#pragma unroll
-      for (int i = 0; i < 64; i += 4) {
-        const float p0 = ex2_approx(fmaf(__uint_as_float(sr[ch * 2 + i / 32][(i + 0) % 32]), cmul, neg_m));
-        const float p1 = ex2_approx(fmaf(__uint_as_float(sr[ch * 2 + i / 32][(i + 1) % 32]), cmul, neg_m));
-        const float p2 = ex2_approx(fmaf(__uint_as_float(sr[ch * 2 + i / 32][(i + 2) % 32]), cmul, neg_m));
-        const float p3 = ex2_approx(fmaf(__uint_as_float(sr[ch * 2 + i / 32][(i + 3) % 32]), cmul, neg_m));
-        l0 += p0;
-        l1 += p1;
-        l2 += p2;
-        l3 += p3;
-        pk[i / 2] = pack2<BF16>(p0, p1);
-        pk[i / 2 + 1] = pack2<BF16>(p2, p3);
-      }
-      tmem_st32(s_addr + ch * 32, pk);
-    }
-    l += (l0 + l1) + (l2 + l3);
-    tmem_st_wait();
-    tc_fence_before();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(p_full);
+    // a block needs element masks only if some row of the tile sees it partially
+    const bool need_mask = (hi_first - j * BN < BN - 1) || (lo_last - j * BN > 0);
+    bool ok;
+    if (need_mask)
+      ok = fwd_softmax_block<Cfg, BF16, SOFTCAP, true>(c, p, s_addr, o_addr, o_full, p_full, n, lo_key - j * BN,
+                                                       hi_key - j * BN, cmul, m, l);
+    else
+      ok = fwd_softmax_block<Cfg, BF16, SOFTCAP, false>(c, p, s_addr, o_addr, o_full, p_full, n, 0, 0, cmul, m, l);
+    if (!ok) return;
   }
 
   // epilogue: O / l -> 16-bit -> global (BSHD), base-2 LSE for the score passes
@@ -422,11 +460,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   c.tmem_base = *tmem_slot;
 
   if (warp < NQ * 4) {
-    fwd_softmax<Cfg, BF16, SOFTCAP>(c, p, warp >> 2);
-  } else if (warp == NQ * 4) {
-    if (lane == 0) fwd_producer<Cfg, BF16>(c, &tm_q, &tm_k, &tm_v);
+    if constexpr (Cfg::REBALANCE_REGS) reg_alloc<224>();
+    if constexpr (NQ == 2) {
+      // the tile index is a compile-time constant inside each branch (no dynamic indexing of per-tile state)
+      if (warp < 4)
+        fwd_softmax<Cfg, BF16, SOFTCAP>(c, p, 0);
+      else
+        fwd_softmax<Cfg, BF16, SOFTCAP>(c, p, 1);
+    } else {
+      fwd_softmax<Cfg, BF16, SOFTCAP>(c, p, 0);
+    }
   } else {
-    if (lane == 0) fwd_mma<Cfg, BF16>(c);
+    if constexpr (Cfg::REBALANCE_REGS) reg_dealloc<56>();
+    if (warp == NQ * 4) {
+      if (lane == 0) fwd_producer<Cfg, BF16>(c, &tm_q, &tm_k, &tm_v);
+    } else if (warp == NQ * 4 + 1) {
+      if (lane == 0) fwd_mma<Cfg, BF16>(c);
+    }
   }
 
   tc_fence_before();

