@@ -57,7 +57,7 @@ struct FwdCfg {
   static constexpr int BAR_V_FULL = BAR_K_EMPTY + STAGES;
   static constexpr int BAR_V_EMPTY = BAR_V_FULL + STAGES;
   static constexpr int BAR_DRAIN = BAR_V_EMPTY + STAGES;
-  static constexpr int NUM_BARS = BAR_DRAIN + 1;
+  static constexpr int NUM_BARS = BAR_DRAIN + NQ;            // one drain barrier per MMA issuer
   static constexpr int SMEM_TILES = NQ * Q_TILE_BYTES + 2 * STAGES * KV_STAGE_BYTES;
   static constexpr int SMEM_BYTES = SMEM_TILES + NUM_BARS * 8 + 16 + 1024;  // +1024: manual alignment slack
 };
@@ -154,83 +154,109 @@ __device__ __forceinline__ void fwd_producer(const FwdCtx<Cfg, BF16>& c, const C
 }
 
 // -------------------------------- MMA issuer --------------------------------
-template <class Cfg, bool BF16>
+// One issuing thread PER QUERY TILE (its own warp): the two tiles' chains
+//   softmax(j) -> P -> [O += P V(j)] -> [S(j+1) = Q K(j+1)^T] -> softmax(j+1)
+// then advance independently, and neither waits behind the other tile's instruction issue.  Both issuers walk
+// every key block of the CTA and both arrive on the K/V "stage empty" barriers (count NQ) -- for blocks outside
+// a tile's visible range the arrive is immediate.
+template <class Cfg, bool BF16, int T>
 __device__ __forceinline__ void fwd_mma(const FwdCtx<Cfg, BF16>& c) {
-  constexpr int ST = Cfg::STAGES, D = Cfg::D, BN = Cfg::BN, BM = Cfg::BM, NQ = Cfg::NQ;
+  constexpr int ST = Cfg::STAGES, D = Cfg::D, BN = Cfg::BN, BM = Cfg::BM;
   constexpr uint32_t IDESC_S = make_idesc(BF16, BM, BN, false, false);
   constexpr uint32_t IDESC_PV = make_idesc(BF16, BM, D, false, true);
   // descriptor halves: the upper word is constant, the lower word is (address >> 4) plus a compile-time step
-  constexpr uint32_t DESC_HI = smem_desc_hi(1024);
-  const uint32_t q_lo = smem_desc_lo(smem_u32(c.sQ), 16);
+  const uint32_t desc_hi = smem_desc_hi(1024);
+  const uint32_t q_lo = smem_desc_lo(smem_u32(c.sQ) + T * Cfg::Q_TILE_BYTES, 16);
   const uint32_t k_lo = smem_desc_lo(smem_u32(c.sK), 16);
   const uint32_t v_lo = smem_desc_lo(smem_u32(c.sV), BN * 128);   // MN-major: LBO = bytes between 64-wide column blocks
-  int k_ready = c.jmin - 1, v_ready = c.jmin - 1;  // last block whose K / V stage has been observed full
-  bool ok = true;
+  const uint32_t s_tmem = c.tmem_base + T * BN;                   // S tile; P (packed 16-bit) overwrites its first half
+  const uint32_t o_tmem = c.tmem_base + Cfg::O_BASE + T * D;
+  const int lo = c.rng[T].lo, hi = c.rng[T].hi;
+  uint64_t* s_full = &c.bars[Cfg::BAR_S_FULL + T];
+  uint64_t* p_full = &c.bars[Cfg::BAR_P_FULL + T];
+  uint64_t* o_full = &c.bars[Cfg::BAR_O_FULL + T];
 
-  auto issue_s = [&](int t, int j) {
-    const int n = j - c.jmin, st = n % ST;
-    if (j == c.rng[t].lo) ok = ok && mbar_wait(&c.bars[Cfg::BAR_Q_FULL + t], 0, c.abort_flag, WAIT_Q_FULL);
-    if (ok && k_ready < j) {
-      ok = mbar_wait(&c.bars[Cfg::BAR_K_FULL + st], (n / ST) & 1, c.abort_flag, WAIT_K_FULL);
-      k_ready = j;
-    }
-    if (!ok) return;
-    tc_fence_after();
-    const uint32_t d_tmem = c.tmem_base + t * BN;
-    const uint32_t a0 = q_lo + (uint32_t)(t * (Cfg::Q_TILE_BYTES >> 4));
+  auto issue_s = [&](int st) {
     const uint32_t b0 = k_lo + (uint32_t)(st * (Cfg::KV_STAGE_BYTES >> 4));
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
       const uint32_t a_off = (uint32_t)(((kk / 4) * (BM * 128) + (kk % 4) * 32) >> 4);
       const uint32_t b_off = (uint32_t)(((kk / 4) * (BN * 128) + (kk % 4) * 32) >> 4);
-      umma_ss(d_tmem, desc_from_halves(a0 + a_off, DESC_HI), desc_from_halves(b0 + b_off, DESC_HI), IDESC_S,
-              kk > 0 ? 1u : 0u);
+      if (kk == 0)
+        umma_ss_c<IDESC_S, 0>(s_tmem, q_lo + a_off, b0 + b_off, desc_hi);
+      else
+        umma_ss_c<IDESC_S, 1>(s_tmem, q_lo + a_off, b0 + b_off, desc_hi);
     }
-    umma_commit(&c.bars[Cfg::BAR_S_FULL + t]);
+    umma_commit(s_full);
   };
-  auto issue_pv = [&](int t, int j) {
-    const int n = j - c.jmin, st = n % ST;
-    ok = ok && mbar_wait(&c.bars[Cfg::BAR_P_FULL + t], (j - c.rng[t].lo) & 1, c.abort_flag, WAIT_P_FULL);
-    if (ok && v_ready < j) {
-      ok = mbar_wait(&c.bars[Cfg::BAR_V_FULL + st], (n / ST) & 1, c.abort_flag, WAIT_V_FULL);
-      v_ready = j;
-    }
-    if (!ok) return;
-    tc_fence_after();
-    const uint32_t d_tmem = c.tmem_base + Cfg::O_BASE + t * D;
-    const uint32_t a_tmem = c.tmem_base + t * BN;  // P: packed 16-bit pairs, 8 columns per 16 keys
+  auto issue_pv = [&](int st, bool first) {
     const uint32_t b0 = v_lo + (uint32_t)(st * (Cfg::KV_STAGE_BYTES >> 4));
-    const uint32_t first = (j > c.rng[t].lo) ? 1u : 0u;
+    // V stage: KSUB column blocks of [BN keys][64 dims]; 16 keys = 2048 bytes further down; P: 8 columns per 16 keys
+    if (first)
+      umma_ts_c<IDESC_PV, 0>(o_tmem, s_tmem, b0, desc_hi);
+    else
+      umma_ts_c<IDESC_PV, 1>(o_tmem, s_tmem, b0, desc_hi);
 #pragma unroll
-    for (int kk = 0; kk < BN / 16; ++kk) {
-      // V stage: KSUB column blocks of [BN keys][64 dims]; 16 keys = 2048 bytes further down
-      umma_ts(d_tmem, a_tmem + kk * 8, desc_from_halves(b0 + (uint32_t)(kk * (2048 >> 4)), DESC_HI), IDESC_PV,
-              kk > 0 ? 1u : first);
-    }
-    umma_commit(&c.bars[Cfg::BAR_O_FULL + t]);
+    for (int kk = 1; kk < BN / 16; ++kk)
+      umma_ts_c<IDESC_PV, 1>(o_tmem, s_tmem + kk * 8, b0 + (uint32_t)(kk * (2048 >> 4)), desc_hi);
+    umma_commit(o_full);
   };
-  auto active = [&](int t, int j) { return j >= c.rng[t].lo && j < c.rng[t].hi; };
 
-  // prologue: S of the first block
-#pragma unroll
-  for (int t = 0; t < NQ; ++t)
-    if (ok && active(t, c.jmin)) issue_s(t, c.jmin);
-  if (ok && c.jmax > c.jmin) umma_commit(&c.bars[Cfg::BAR_K_EMPTY + 0]);
-
-  for (int j = c.jmin; j < c.jmax && ok; ++j) {
-    const int n = j - c.jmin;
-#pragma unroll
-    for (int t = 0; t < NQ; ++t) {
-      if (ok && active(t, j)) issue_pv(t, j);
-      if (ok && active(t, j + 1)) issue_s(t, j + 1);
+  // All 32 lanes walk the loop (warp-uniform), one elected lane issues.  Every block's stage is waited for
+  // (FULL) before this issuer releases it (EMPTY), also for blocks outside the tile's range: an issuer can
+  // therefore never run more than the ring depth ahead of the other one, which keeps the count-NQ EMPTY
+  // barriers phase-exact.
+  bool ok = true;
+  if (c.jmax > c.jmin) {
+    ok = mbar_wait(&c.bars[Cfg::BAR_K_FULL + 0], 0, c.abort_flag, WAIT_K_FULL);
+    if (ok && c.jmin >= lo && c.jmin < hi) {
+      ok = mbar_wait(&c.bars[Cfg::BAR_Q_FULL + T], 0, c.abort_flag, WAIT_Q_FULL);
+      if (ok) {
+        tc_fence_after();
+        if (elect_one()) issue_s(0);
+      }
     }
+    if (ok && elect_one()) umma_commit(&c.bars[Cfg::BAR_K_EMPTY + 0]);
+    __syncwarp();
+  }
+  for (int j = c.jmin; j < c.jmax && ok; ++j) {
+    const int n = j - c.jmin, st = n % ST, ph = (n / ST) & 1;
+    const bool act = j >= lo && j < hi;
+    if (act) ok = mbar_wait(p_full, (j - lo) & 1, c.abort_flag, WAIT_P_FULL);
+    ok = ok && mbar_wait(&c.bars[Cfg::BAR_V_FULL + st], ph, c.abort_flag, WAIT_V_FULL);
     if (!ok) break;
-    umma_commit(&c.bars[Cfg::BAR_V_EMPTY + n % ST]);                          // V(j) consumed
-    if (j + 1 < c.jmax) umma_commit(&c.bars[Cfg::BAR_K_EMPTY + (n + 1) % ST]);  // K(j+1) consumed
+    tc_fence_after();
+    if (elect_one()) {
+      if (act) {
+        B200_TL((2 * 64 + (n & 63)) * 8 + T * 4 + 0);
+        issue_pv(st, j == lo);
+        B200_TL((2 * 64 + (n & 63)) * 8 + T * 4 + 1);
+      }
+      umma_commit(&c.bars[Cfg::BAR_V_EMPTY + st]);   // V(j) consumed by this tile
+    }
+    __syncwarp();
+    if (j + 1 < c.jmax) {
+      const int n1 = n + 1, st1 = n1 % ST, ph1 = (n1 / ST) & 1;
+      const bool act1 = j + 1 >= lo && j + 1 < hi;
+      if (act1 && j + 1 == lo) ok = mbar_wait(&c.bars[Cfg::BAR_Q_FULL + T], 0, c.abort_flag, WAIT_Q_FULL);
+      ok = ok && mbar_wait(&c.bars[Cfg::BAR_K_FULL + st1], ph1, c.abort_flag, WAIT_K_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      if (elect_one()) {
+        if (act1) {
+          B200_TL((2 * 64 + (n1 & 63)) * 8 + T * 4 + 2);
+          issue_s(st1);
+          B200_TL((2 * 64 + (n1 & 63)) * 8 + T * 4 + 3);
+        }
+        umma_commit(&c.bars[Cfg::BAR_K_EMPTY + st1]);  // K(j+1) consumed by this tile
+      }
+      __syncwarp();
+    }
   }
   // every MMA issued above has retired before the CTA tears TMEM down
-  umma_commit(&c.bars[Cfg::BAR_DRAIN]);
-  mbar_wait(&c.bars[Cfg::BAR_DRAIN], 0, c.abort_flag, WAIT_DRAIN);
+  if (elect_one()) umma_commit(&c.bars[Cfg::BAR_DRAIN + T]);
+  __syncwarp();
+  mbar_wait(&c.bars[Cfg::BAR_DRAIN + T], 0, c.abort_flag, WAIT_DRAIN);
 }
 
 // ------------------------------ softmax warpgroup ----------------------------
@@ -241,10 +267,14 @@ __device__ __forceinline__ bool fwd_softmax_block(const FwdCtx<Cfg, BF16>& c, co
                                                   int lo_c, int hi_c, float cmul, float& m, float& l) {
   constexpr int D = Cfg::D, BN = Cfg::BN;
   const int lane = threadIdx.x & 31;
+  const int tl_base = (((int)(threadIdx.x >> 7)) * 64 + (n & 63)) * 8;
+  const bool tl_on = (threadIdx.x & 127) == 0;
+  if (tl_on) B200_TL(tl_base + 0);
   uint32_t sr[BN / 32][32];
 #pragma unroll
   for (int ch = 0; ch < BN / 32; ++ch) tmem_ld32(s_addr + ch * 32, sr[ch]);
   tmem_ld_wait();
+  if (tl_on) B200_TL(tl_base + 1);
 
   float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -268,6 +298,7 @@ __device__ __forceinline__ bool fwd_softmax_block(const FwdCtx<Cfg, BF16>& c, co
     }
   }
   const float m_blk = fmaxf(mx0, mx1) * cmul;  // -inf when the whole row is masked inside this block
+  if (tl_on) B200_TL(tl_base + 2);
   float alpha = 1.0f;
   bool rescale = false;
   if (n == 0) {
@@ -320,10 +351,12 @@ __device__ __forceinline__ bool fwd_softmax_block(const FwdCtx<Cfg, BF16>& c, co
     tmem_st16(s_addr + ch * 16, pk);
   }
   l += (acc0.x + acc0.y) + (acc1.x + acc1.y);
+  if (tl_on) B200_TL(tl_base + 3);
   tmem_st_wait();
   tc_fence_before();
   __syncwarp();
   if (lane == 0) mbar_arrive(p_full);
+  if (tl_on) B200_TL(tl_base + 4);
   return true;
 }
 
@@ -439,8 +472,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (threadIdx.x == 0) {
 #pragma unroll
     for (int i = 0; i < Cfg::NUM_BARS; ++i) {
-      const bool is_p_full = (i >= Cfg::BAR_P_FULL && i < Cfg::BAR_P_FULL + NQ);
-      mbar_init(&c.bars[i], is_p_full ? 4u : 1u);
+      const bool is_p_full = (i >= Cfg::BAR_P_FULL && i < Cfg::BAR_P_FULL + NQ);               // 4 softmax warps
+      const bool is_empty = (i >= Cfg::BAR_K_EMPTY && i < Cfg::BAR_K_EMPTY + Cfg::STAGES) ||
+                            (i >= Cfg::BAR_V_EMPTY && i < Cfg::BAR_V_EMPTY + Cfg::STAGES);      // NQ MMA issuers
+      mbar_init(&c.bars[i], is_p_full ? 4u : is_empty ? (uint32_t)NQ : 1u);
     }
     *c.abort_flag = 0;
     fence_mbar_init();
@@ -475,7 +510,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (warp == NQ * 4) {
       if (lane == 0) fwd_producer<Cfg, BF16>(c, &tm_q, &tm_k, &tm_v);
     } else if (warp == NQ * 4 + 1) {
-      if (lane == 0) fwd_mma<Cfg, BF16>(c);
+      fwd_mma<Cfg, BF16, 0>(c);
+    } else if (NQ == 2 && warp == NQ * 4 + 2) {
+      fwd_mma<Cfg, BF16, NQ - 1>(c);
     }
   }
 

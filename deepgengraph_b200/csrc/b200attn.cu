@@ -204,4 +204,14 @@ int b200_attn_kf_score(const void* q, const void* k, const void* v, const float*
                       head_dim, dtype, causal, tau, scale, (cudaStream_t)stream);
 }
 
+#ifdef B200_TIMELINE
+// tuning builds only: where selected threads of CTA `block` stamp their phase clocks
+int b200_debug_set_timeline(void* buffer, int block) {
+  long long* p = (long long*)buffer;
+  B200_CUDA_TRY(cudaMemcpyToSymbol(g_timeline, &p, sizeof(p)));
+  B200_CUDA_TRY(cudaMemcpyToSymbol(g_timeline_block, &block, sizeof(int)));
+  return B200_OK;
+}
+#endif
+
 }  // extern "C"

@@ -36,6 +36,20 @@ inline thread_local int g_last_cuda_error = 0;
 // record the first expired wait here instead of spinning forever.
 __device__ int g_device_status = 0;
 
+// Optional phase timeline for kernel tuning (compiled in with -DB200_TIMELINE only): selected threads of one
+// CTA stamp clock64() into a caller-provided buffer.
+#ifdef B200_TIMELINE
+__device__ long long* g_timeline = nullptr;
+__device__ int g_timeline_block = 0;
+#define B200_TL(slot)                                                                                  \
+  do {                                                                                                 \
+    if (g_timeline != nullptr && (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) == g_timeline_block) \
+      g_timeline[(slot)] = clock64();                                                                  \
+  } while (0)
+#else
+#define B200_TL(slot) do { } while (0)
+#endif
+
 // codes stored in the low byte of the status word
 enum WaitCode : int {
   WAIT_Q_FULL = 1,
@@ -60,6 +74,18 @@ enum WaitCode : int {
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// One lane of a converged warp.  Role loops run on ALL lanes (warp-uniform control flow keeps their address and
+// descriptor arithmetic on the uniform datapath) and only the instruction that must be issued once is guarded.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
 }
 
 __device__ __forceinline__ uint64_t global_timer_ns() {
@@ -235,6 +261,29 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Same with the accumulate flag and the instruction descriptor as compile-time constants (the predicate folds
+// away: an MMA issuer is a single thread, every instruction it does not execute is latency off the chain).
+template <uint32_t IDESC, int ACC>
+__device__ __forceinline__ void umma_ss_c(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "n"(IDESC), "n"(ACC)
+      : "memory");
+}
+template <uint32_t IDESC, int ACC>
+__device__ __forceinline__ void umma_ts_c(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t desc_hi) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(desc_hi), "n"(IDESC), "n"(ACC)
       : "memory");
 }
 
