@@ -1,18 +1,17 @@
 // Fused attention forward for sm_100a:  out = softmax(mask(softcap(q k^T * scale))) v.
 //
-// One CTA owns NQ query tiles of 128 rows of one (batch, head) and walks the key/value
-// blocks that the causal / sliding-window mask leaves visible.  Roles (warp-specialised):
-//   warps [0, 4*NQ)   softmax warpgroups, one per query tile: thread r of a group owns row r
-//                     (TMEM lane r) -- online softmax, O rescale, epilogue
-//   warp  4*NQ        TMA producer (one lane): Q once, then a ring of K and V stages
-//   warp  4*NQ + 1    MMA issuer (one lane): S = Q K^T (operands in shared memory) and
-//                     O += P V (P read from TMEM, V from shared memory) on tcgen05
-// TMEM columns: [S tile per query tile (fp32, BN columns; the 16-bit P overwrites its first
-// BN/2 columns)] [O accumulator per query tile (fp32, D columns)].
+// One CTA owns NQ query tiles of 128 rows of one (batch, head) and walks the key/value blocks that the
+// causal / sliding-window mask leaves visible.  Roles (warp-specialised):
+//   warps [0, 4*NQ)      softmax warpgroups, one per query tile: thread r of a group owns row r (TMEM lane r)
+//                        -- online softmax, O rescale, epilogue
+//   warp  4*NQ           TMA producer: Q once, then K(j), V(j), K(j+1), ... through ONE ring of SLOTS stages
+//   warps 4*NQ+1 (+2)    MMA issuers, one per query tile: S = Q K^T (operands in shared memory) and
+//                        O += P V (P read from TMEM, V from shared memory) on tcgen05
+// TMEM columns: [S tile per query tile (fp32, BN columns; the 16-bit P overwrites its first BN/2 columns)]
+//               [O accumulator per query tile (fp32, D columns)].
 //
-// Reference semantics: deepgengraph_exp/cases/kernels/attn.py:18-34 (mask, scale, fp32
-// softmax, P rounded to the input type before P V) and kernels/gemma2.py:30-34 (soft-cap
-// after the scale, before the mask).
+// Reference semantics: deepgengraph_exp/cases/kernels/attn.py:18-34 (mask, scale, fp32 softmax, P rounded to
+// the input type before P V) and kernels/gemma2.py:30-34 (soft-cap after the scale, before the mask).
 #pragma once
 
 #include "common.cuh"
@@ -35,10 +34,13 @@ template <int D_, int BN_, int NQ_>
 struct FwdCfg {
   static constexpr int D = D_, BN = BN_, NQ = NQ_;
   static constexpr int BM = 128;
-  static constexpr int STAGES = 2;
   static constexpr int KSUB = D / 64;                 // 64-element (128-byte) column blocks of a row
   static constexpr int Q_TILE_BYTES = BM * D * 2;
   static constexpr int KV_STAGE_BYTES = BN * D * 2;
+  // one ring for K and V blocks (K(j) is item 2n, V(j) item 2n+1): as many slots as fit beside Q, at most 6
+  static constexpr int SLOTS_FIT = (232448 - 2048 - NQ * Q_TILE_BYTES) / KV_STAGE_BYTES;
+  static constexpr int SLOTS = SLOTS_FIT > 6 ? 6 : SLOTS_FIT;
+  static_assert(SLOTS >= 3, "ring too shallow");
   static constexpr int O_BASE = ((NQ * BN + D - 1) / D) * D;
   static constexpr int TMEM_USED = O_BASE + NQ * D;
   static constexpr int TMEM_COLS = TMEM_USED <= 32 ? 32 : TMEM_USED <= 64 ? 64 : TMEM_USED <= 128 ? 128
@@ -52,14 +54,14 @@ struct FwdCfg {
   static constexpr int BAR_S_FULL = BAR_Q_FULL + NQ;         // [NQ]
   static constexpr int BAR_P_FULL = BAR_S_FULL + NQ;         // [NQ]
   static constexpr int BAR_O_FULL = BAR_P_FULL + NQ;         // [NQ]
-  static constexpr int BAR_K_FULL = BAR_O_FULL + NQ;         // [STAGES]
-  static constexpr int BAR_K_EMPTY = BAR_K_FULL + STAGES;
-  static constexpr int BAR_V_FULL = BAR_K_EMPTY + STAGES;
-  static constexpr int BAR_V_EMPTY = BAR_V_FULL + STAGES;
-  static constexpr int BAR_DRAIN = BAR_V_EMPTY + STAGES;
-  static constexpr int NUM_BARS = BAR_DRAIN + NQ;            // one drain barrier per MMA issuer
-  static constexpr int SMEM_TILES = NQ * Q_TILE_BYTES + 2 * STAGES * KV_STAGE_BYTES;
+  static constexpr int BAR_FULL = BAR_O_FULL + NQ;           // [SLOTS]
+  static constexpr int BAR_EMPTY = BAR_FULL + SLOTS;         // [SLOTS]
+  static constexpr int BAR_DRAIN = BAR_EMPTY + SLOTS;        // [NQ] one drain barrier per MMA issuer
+  static constexpr int BAR_TURN = BAR_DRAIN + NQ;            // [NQ][4]: exp-phase turn of softmax warp w of tile t
+  static constexpr int NUM_BARS = BAR_TURN + NQ * 4;
+  static constexpr int SMEM_TILES = NQ * Q_TILE_BYTES + SLOTS * KV_STAGE_BYTES;
   static constexpr int SMEM_BYTES = SMEM_TILES + NUM_BARS * 8 + 16 + 1024;  // +1024: manual alignment slack
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget exceeded");
 };
 
 // Block range of one query tile: key blocks [lo, hi) hold at least one visible key.
@@ -82,8 +84,7 @@ __device__ __forceinline__ TileRange tile_range(int r_first, int bn, const FwdPa
 template <class Cfg, bool BF16>
 struct FwdCtx {
   uint8_t* sQ;
-  uint8_t* sK;
-  uint8_t* sV;
+  uint8_t* sKV;
   uint64_t* bars;
   volatile int* abort_flag;
   uint32_t tmem_base;
@@ -96,7 +97,7 @@ struct FwdCtx {
 template <class Cfg, bool BF16>
 __device__ __forceinline__ void fwd_producer(const FwdCtx<Cfg, BF16>& c, const CUtensorMap* tm_q,
                                              const CUtensorMap* tm_k, const CUtensorMap* tm_v) {
-  constexpr int ST = Cfg::STAGES;
+  constexpr int SL = Cfg::SLOTS;
 #pragma unroll
   for (int t = 0; t < Cfg::NQ; ++t) {
     if (c.rng[t].hi > c.rng[t].lo) {
@@ -107,42 +108,33 @@ __device__ __forceinline__ void fwd_producer(const FwdCtx<Cfg, BF16>& c, const C
                     ks * 64, c.h, c.q0 + t * Cfg::BM, c.b);
     }
   }
+  const int items = 2 * (c.jmax - c.jmin);   // K(j) is ring item 2n, V(j) item 2n+1, n = j - jmin
   int issued = 0;
   bool ok = true;
-  for (int j = c.jmin; j < c.jmax && ok; ++j) {
-    const int n = j - c.jmin, st = n % ST, use = n / ST;
-    if (use > 0) ok = mbar_wait(&c.bars[Cfg::BAR_K_EMPTY + st], (use - 1) & 1, c.abort_flag, WAIT_K_EMPTY);
-    if (!ok) break;
-    mbar_expect_tx(&c.bars[Cfg::BAR_K_FULL + st], Cfg::KV_STAGE_BYTES);
-#pragma unroll
-    for (int ks = 0; ks < Cfg::KSUB; ++ks)
-      tma_load_4d(c.sK + st * Cfg::KV_STAGE_BYTES + ks * (Cfg::BN * 128), tm_k, &c.bars[Cfg::BAR_K_FULL + st],
-                  ks * 64, c.hk, j * Cfg::BN, c.b);
-    if (use > 0) ok = mbar_wait(&c.bars[Cfg::BAR_V_EMPTY + st], (use - 1) & 1, c.abort_flag, WAIT_V_EMPTY);
-    if (!ok) {
-      issued = n * 2 + 1;
+  for (int i = 0; i < items; ++i) {
+    const int slot = i % SL, use = i / SL, j = c.jmin + (i >> 1);
+    if (use > 0 && !mbar_wait(&c.bars[Cfg::BAR_EMPTY + slot], (use - 1) & 1, c.abort_flag, WAIT_K_EMPTY)) {
+      ok = false;
       break;
     }
-    mbar_expect_tx(&c.bars[Cfg::BAR_V_FULL + st], Cfg::KV_STAGE_BYTES);
+    uint64_t* full = &c.bars[Cfg::BAR_FULL + slot];
+    uint8_t* dst = c.sKV + slot * Cfg::KV_STAGE_BYTES;
+    const CUtensorMap* tm = (i & 1) ? tm_v : tm_k;
+    mbar_expect_tx(full, Cfg::KV_STAGE_BYTES);
 #pragma unroll
     for (int ks = 0; ks < Cfg::KSUB; ++ks)
-      tma_load_4d(c.sV + st * Cfg::KV_STAGE_BYTES + ks * (Cfg::BN * 128), tm_v, &c.bars[Cfg::BAR_V_FULL + st],
-                  ks * 64, c.hk, j * Cfg::BN, c.b);
-    issued = n * 2 + 2;
+      tma_load_4d(dst + ks * (Cfg::BN * 128), tm, full, ks * 64, c.hk, j * Cfg::BN, c.b);
+    issued = i + 1;
   }
   if (!ok || *c.abort_flag != 0) {
-    // Abort path: do not leave the CTA while our own bulk copies may still be landing in
-    // shared memory.  Wait (bounded, 20 ms) for the most recent load of every stage.
+    // Abort path: do not leave the CTA while our own bulk copies may still be landing in shared memory.
+    // Wait (bounded, 20 ms) for the most recent load of every slot and for the Q tiles.
     const uint64_t t0 = global_timer_ns();
-    const int nk = (issued + 1) / 2, nv = issued / 2;  // K loads, V loads issued
-    for (int st = 0; st < ST; ++st) {
-      const int uk = (nk - 1 - st) >= 0 ? (nk - 1 - st) / ST : -1;  // last use index of stage st for K
-      const int uv = (nv - 1 - st) >= 0 ? (nv - 1 - st) / ST : -1;
-      while (uk >= 0 && !mbar_try_wait(&c.bars[Cfg::BAR_K_FULL + st], uk & 1) &&
-             global_timer_ns() - t0 < 20000000ull) {
-      }
-      while (uv >= 0 && !mbar_try_wait(&c.bars[Cfg::BAR_V_FULL + st], uv & 1) &&
-             global_timer_ns() - t0 < 20000000ull) {
+    for (int slot = 0; slot < SL; ++slot) {
+      if (issued <= slot) continue;
+      const int last = slot + ((issued - 1 - slot) / SL) * SL;   // last item that used `slot`
+      const int u = last / SL;
+      while (!mbar_try_wait(&c.bars[Cfg::BAR_FULL + slot], u & 1) && global_timer_ns() - t0 < 20000000ull) {
       }
     }
 #pragma unroll
@@ -161,14 +153,14 @@ __device__ __forceinline__ void fwd_producer(const FwdCtx<Cfg, BF16>& c, const C
 // a tile's visible range the arrive is immediate.
 template <class Cfg, bool BF16, int T>
 __device__ __forceinline__ void fwd_mma(const FwdCtx<Cfg, BF16>& c) {
-  constexpr int ST = Cfg::STAGES, D = Cfg::D, BN = Cfg::BN, BM = Cfg::BM;
+  constexpr int SL = Cfg::SLOTS, D = Cfg::D, BN = Cfg::BN, BM = Cfg::BM;
   constexpr uint32_t IDESC_S = make_idesc(BF16, BM, BN, false, false);
   constexpr uint32_t IDESC_PV = make_idesc(BF16, BM, D, false, true);
   // descriptor halves: the upper word is constant, the lower word is (address >> 4) plus a compile-time step
   const uint32_t desc_hi = smem_desc_hi(1024);
   const uint32_t q_lo = smem_desc_lo(smem_u32(c.sQ) + T * Cfg::Q_TILE_BYTES, 16);
-  const uint32_t k_lo = smem_desc_lo(smem_u32(c.sK), 16);
-  const uint32_t v_lo = smem_desc_lo(smem_u32(c.sV), BN * 128);   // MN-major: LBO = bytes between 64-wide column blocks
+  const uint32_t k_lo = smem_desc_lo(smem_u32(c.sKV), 16);
+  const uint32_t v_lo = smem_desc_lo(smem_u32(c.sKV), BN * 128);   // MN-major: LBO = bytes between 64-wide column blocks
   const uint32_t s_tmem = c.tmem_base + T * BN;                   // S tile; P (packed 16-bit) overwrites its first half
   const uint32_t o_tmem = c.tmem_base + Cfg::O_BASE + T * D;
   const int lo = c.rng[T].lo, hi = c.rng[T].hi;
@@ -176,8 +168,8 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<Cfg, BF16>& c) {
   uint64_t* p_full = &c.bars[Cfg::BAR_P_FULL + T];
   uint64_t* o_full = &c.bars[Cfg::BAR_O_FULL + T];
 
-  auto issue_s = [&](int st) {
-    const uint32_t b0 = k_lo + (uint32_t)(st * (Cfg::KV_STAGE_BYTES >> 4));
+  auto issue_s = [&](int slot) {
+    const uint32_t b0 = k_lo + (uint32_t)(slot * (Cfg::KV_STAGE_BYTES >> 4));
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
       const uint32_t a_off = (uint32_t)(((kk / 4) * (BM * 128) + (kk % 4) * 32) >> 4);
@@ -189,8 +181,8 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<Cfg, BF16>& c) {
     }
     umma_commit(s_full);
   };
-  auto issue_pv = [&](int st, bool first) {
-    const uint32_t b0 = v_lo + (uint32_t)(st * (Cfg::KV_STAGE_BYTES >> 4));
+  auto issue_pv = [&](int slot, bool first) {
+    const uint32_t b0 = v_lo + (uint32_t)(slot * (Cfg::KV_STAGE_BYTES >> 4));
     // V stage: KSUB column blocks of [BN keys][64 dims]; 16 keys = 2048 bytes further down; P: 8 columns per 16 keys
     if (first)
       umma_ts_c<IDESC_PV, 0>(o_tmem, s_tmem, b0, desc_hi);
@@ -202,13 +194,13 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<Cfg, BF16>& c) {
     umma_commit(o_full);
   };
 
-  // All 32 lanes walk the loop (warp-uniform), one elected lane issues.  Every block's stage is waited for
-  // (FULL) before this issuer releases it (EMPTY), also for blocks outside the tile's range: an issuer can
-  // therefore never run more than the ring depth ahead of the other one, which keeps the count-NQ EMPTY
-  // barriers phase-exact.
+  // All 32 lanes walk the loop (warp-uniform), one elected lane issues.  Every ring slot is waited for (FULL)
+  // before this issuer releases it (EMPTY), also for blocks outside the tile's range: an issuer can therefore
+  // never run more than the ring depth ahead of the other one, which keeps the count-NQ EMPTY barriers
+  // phase-exact.
   bool ok = true;
-  if (c.jmax > c.jmin) {
-    ok = mbar_wait(&c.bars[Cfg::BAR_K_FULL + 0], 0, c.abort_flag, WAIT_K_FULL);
+  if (c.jmax > c.jmin) {   // prologue: S of the first block (ring item 0)
+    ok = mbar_wait(&c.bars[Cfg::BAR_FULL + 0], 0, c.abort_flag, WAIT_K_FULL);
     if (ok && c.jmin >= lo && c.jmin < hi) {
       ok = mbar_wait(&c.bars[Cfg::BAR_Q_FULL + T], 0, c.abort_flag, WAIT_Q_FULL);
       if (ok) {
@@ -216,39 +208,42 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<Cfg, BF16>& c) {
         if (elect_one()) issue_s(0);
       }
     }
-    if (ok && elect_one()) umma_commit(&c.bars[Cfg::BAR_K_EMPTY + 0]);
+    if (ok && elect_one()) umma_commit(&c.bars[Cfg::BAR_EMPTY + 0]);
     __syncwarp();
   }
   for (int j = c.jmin; j < c.jmax && ok; ++j) {
-    const int n = j - c.jmin, st = n % ST, ph = (n / ST) & 1;
-    const bool act = j >= lo && j < hi;
-    if (act) ok = mbar_wait(p_full, (j - lo) & 1, c.abort_flag, WAIT_P_FULL);
-    ok = ok && mbar_wait(&c.bars[Cfg::BAR_V_FULL + st], ph, c.abort_flag, WAIT_V_FULL);
-    if (!ok) break;
-    tc_fence_after();
-    if (elect_one()) {
-      if (act) {
-        B200_TL((2 * 64 + (n & 63)) * 8 + T * 4 + 0);
-        issue_pv(st, j == lo);
-        B200_TL((2 * 64 + (n & 63)) * 8 + T * 4 + 1);
-      }
-      umma_commit(&c.bars[Cfg::BAR_V_EMPTY + st]);   // V(j) consumed by this tile
-    }
-    __syncwarp();
-    if (j + 1 < c.jmax) {
-      const int n1 = n + 1, st1 = n1 % ST, ph1 = (n1 / ST) & 1;
-      const bool act1 = j + 1 >= lo && j + 1 < hi;
-      if (act1 && j + 1 == lo) ok = mbar_wait(&c.bars[Cfg::BAR_Q_FULL + T], 0, c.abort_flag, WAIT_Q_FULL);
-      ok = ok && mbar_wait(&c.bars[Cfg::BAR_K_FULL + st1], ph1, c.abort_flag, WAIT_K_FULL);
+    const int n = j - c.jmin;
+    {  // O += P(j) V(j): ring item 2n+1
+      const int i = 2 * n + 1, slot = i % SL, ph = (i / SL) & 1;
+      const bool act = j >= lo && j < hi;
+      if (act) ok = mbar_wait(p_full, (j - lo) & 1, c.abort_flag, WAIT_P_FULL);
+      ok = ok && mbar_wait(&c.bars[Cfg::BAR_FULL + slot], ph, c.abort_flag, WAIT_V_FULL);
       if (!ok) break;
       tc_fence_after();
       if (elect_one()) {
-        if (act1) {
-          B200_TL((2 * 64 + (n1 & 63)) * 8 + T * 4 + 2);
-          issue_s(st1);
-          B200_TL((2 * 64 + (n1 & 63)) * 8 + T * 4 + 3);
+        if (act) {
+          B200_TL((2 * 64 + (n & 63)) * 8 + T * 4 + 0);
+          issue_pv(slot, j == lo);
+          B200_TL((2 * 64 + (n & 63)) * 8 + T * 4 + 1);
         }
-        umma_commit(&c.bars[Cfg::BAR_K_EMPTY + st1]);  // K(j+1) consumed by this tile
+        umma_commit(&c.bars[Cfg::BAR_EMPTY + slot]);   // V(j) consumed by this tile
+      }
+      __syncwarp();
+    }
+    if (j + 1 < c.jmax) {  // S(j+1) = Q K(j+1)^T: ring item 2n+2
+      const int i = 2 * n + 2, slot = i % SL, ph = (i / SL) & 1;
+      const bool act = j + 1 >= lo && j + 1 < hi;
+      if (act && j + 1 == lo) ok = mbar_wait(&c.bars[Cfg::BAR_Q_FULL + T], 0, c.abort_flag, WAIT_Q_FULL);
+      ok = ok && mbar_wait(&c.bars[Cfg::BAR_FULL + slot], ph, c.abort_flag, WAIT_K_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      if (elect_one()) {
+        if (act) {
+          B200_TL((2 * 64 + ((n + 1) & 63)) * 8 + T * 4 + 2);
+          issue_s(slot);
+          B200_TL((2 * 64 + ((n + 1) & 63)) * 8 + T * 4 + 3);
+        }
+        umma_commit(&c.bars[Cfg::BAR_EMPTY + slot]);  // K(j+1) consumed by this tile
       }
       __syncwarp();
     }
@@ -260,11 +255,45 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<Cfg, BF16>& c) {
 }
 
 // ------------------------------ softmax warpgroup ----------------------------
+// 2^x for two values on the FMA/ALU pipes (no special-function unit): round x to the nearest integer n with the
+// 1.5 * 2^23 trick, evaluate a cubic minimax polynomial of 2^f on f = x - n in [-0.5, 0.5] (max relative error
+// 7.5e-5, far below the 2^-9 rounding of the 16-bit P), and add n to the exponent field.  x is clamped at -125 so
+// that the exponent never wraps.  Used for a fixed fraction of the columns of every unmasked block: the
+// exponentials of attention are bound by the special-function unit (16 results per clock per SM), and moving
+// part of them to the FMA pipe shortens the softmax phase.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  const float kMagic = 12582912.0f;  // 1.5 * 2^23
+  x.x = fmaxf(x.x, -125.0f);
+  x.y = fmaxf(x.y, -125.0f);
+  const float2 r = fadd2(x, make_float2(kMagic, kMagic));              // low mantissa bits = round(x)
+  const float2 n = fadd2(r, make_float2(-kMagic, -kMagic));            // round(x) as a float
+  const float2 f = fadd2(x, make_float2(-n.x, -n.y));                  // in [-0.5, 0.5]
+  float2 pl = ffma2(f, make_float2(0.0551716648f, 0.0551716648f), make_float2(0.2426111251f, 0.2426111251f));
+  pl = ffma2(pl, f, make_float2(0.6932609677f, 0.6932609677f));
+  pl = ffma2(pl, f, make_float2(0.9999280572f, 0.9999280572f));
+  float2 out;
+  out.x = __uint_as_float(__float_as_uint(pl.x) + (__float_as_uint(r.x) << 23));
+  out.y = __uint_as_float(__float_as_uint(pl.y) + (__float_as_uint(r.y) << 23));
+  return out;
+}
+
+#ifndef B200_POLY_OF_8
+#define B200_POLY_OF_8 0
+#endif
+#ifndef B200_TAKE_TURNS
+#define B200_TAKE_TURNS 0
+#endif
+// Of every 8 groups of 4 columns, this many have their exponentials evaluated on the FMA pipe.
+constexpr int kPolyOf8 = B200_POLY_OF_8;
+// Exp-phase turn-taking between the two query tiles of a CTA (tuning switch).
+constexpr bool kTakeTurns = B200_TAKE_TURNS != 0;
+
 // One block of the online softmax for one row (thread).  MASK selects the edge-block variant.
 template <class Cfg, bool BF16, bool SOFTCAP, bool MASK>
 __device__ __forceinline__ bool fwd_softmax_block(const FwdCtx<Cfg, BF16>& c, const FwdParams& p, uint32_t s_addr,
                                                   uint32_t o_addr, uint64_t* o_full, uint64_t* p_full, int n,
-                                                  int lo_c, int hi_c, float cmul, float& m, float& l) {
+                                                  int lo_c, int hi_c, float cmul, float& m, float& l,
+                                                  uint64_t* turn_wait, int turn_parity, uint64_t* turn_pass) {
   constexpr int D = Cfg::D, BN = Cfg::BN;
   const int lane = threadIdx.x & 31;
   const int tl_base = (((int)(threadIdx.x >> 7)) * 64 + (n & 63)) * 8;
@@ -329,6 +358,10 @@ __device__ __forceinline__ bool fwd_softmax_block(const FwdCtx<Cfg, BF16>& c, co
       tmem_st16(o_addr + ch * 16, o);
     }
   }
+  // The exponentials saturate the special-function unit, which the warp of the other query tile on this SM
+  // sub-partition shares: the two take turns (see fwd_softmax), so that one tile's exponentials overlap the
+  // other tile's MMAs instead of colliding with its exponentials.
+  if (turn_wait != nullptr && !mbar_wait(turn_wait, turn_parity, c.abort_flag, WAIT_TURN)) return false;
   // P = exp2(x - m), packed to the 16-bit input type, written over the first BN/2 columns of S
   const float2 c2 = make_float2(cmul, cmul), nm2 = make_float2(-m, -m);
   float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
@@ -339,10 +372,17 @@ __device__ __forceinline__ bool fwd_softmax_block(const FwdCtx<Cfg, BF16>& c, co
     for (int i = 0; i < 32; i += 4) {
       float2 x0 = ffma2(make_float2(__uint_as_float(sr[ch][i + 0]), __uint_as_float(sr[ch][i + 1])), c2, nm2);
       float2 x1 = ffma2(make_float2(__uint_as_float(sr[ch][i + 2]), __uint_as_float(sr[ch][i + 3])), c2, nm2);
-      x0.x = ex2_approx(x0.x);
-      x0.y = ex2_approx(x0.y);
-      x1.x = ex2_approx(x1.x);
-      x1.y = ex2_approx(x1.y);
+      // masked blocks hold -inf entries and stay on the special-function unit; elsewhere a fixed, interleaved
+      // subset of the column groups goes through the polynomial
+      if (!MASK && (((i / 4) * kPolyOf8) % 8) < kPolyOf8) {
+        x0 = exp2_poly2(x0);
+        x1 = exp2_poly2(x1);
+      } else {
+        x0.x = ex2_approx(x0.x);
+        x0.y = ex2_approx(x0.y);
+        x1.x = ex2_approx(x1.x);
+        x1.y = ex2_approx(x1.y);
+      }
       acc0 = fadd2(acc0, x0);
       acc1 = fadd2(acc1, x1);
       pk[i / 2] = pack2<BF16>(x0.x, x0.y);
@@ -351,6 +391,10 @@ __device__ __forceinline__ bool fwd_softmax_block(const FwdCtx<Cfg, BF16>& c, co
     tmem_st16(s_addr + ch * 16, pk);
   }
   l += (acc0.x + acc0.y) + (acc1.x + acc1.y);
+  if (turn_pass != nullptr) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(turn_pass);
+  }
   if (tl_on) B200_TL(tl_base + 3);
   tmem_st_wait();
   tc_fence_before();
@@ -384,18 +428,40 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<Cfg, BF16>& c, const Fw
   const int hi_first = p.causal ? min(r_tile + p.delta, p.kv_len - 1) : p.kv_len - 1;          // first row of the tile
   const int lo_last = (p.causal && p.window > 0) ? (r_tile + 127 + p.delta - p.window + 1) : -(1 << 28);  // last row
 
+  // Turn-taking of the exponential phases between warp w of tile 0 and warp w of tile 1 (same SM sub-partition):
+  // tile 0 runs its i-th phase after tile 1's (i-1)-th, tile 1 its i-th after tile 0's i-th.  A tile only waits
+  // for phases the other tile really has (their block counts differ under a causal mask).
+  uint64_t* turn_mine = nullptr;
+  uint64_t* turn_other = nullptr;
+  int n_other = 0;
+  if constexpr (Cfg::NQ == 2 && kTakeTurns) {
+    turn_mine = &c.bars[Cfg::BAR_TURN + t * 4 + warp_q];
+    turn_other = &c.bars[Cfg::BAR_TURN + (1 - t) * 4 + warp_q];
+    n_other = c.rng[1 - t].hi - c.rng[1 - t].lo;
+  }
+
   for (int j = rng.lo; j < rng.hi; ++j) {
     const int n = j - rng.lo;
     if (!mbar_wait(s_full, n & 1, c.abort_flag, WAIT_S_FULL)) return;
     tc_fence_after();
     // a block needs element masks only if some row of the tile sees it partially
     const bool need_mask = (hi_first - j * BN < BN - 1) || (lo_last - j * BN > 0);
+    uint64_t* tw = nullptr;
+    int tpar = 0;
+    if constexpr (Cfg::NQ == 2 && kTakeTurns) {
+      const int need = (t == 0) ? n - 1 : n;          // index of the other tile's phase that must be over
+      if (need >= 0 && need < n_other) {
+        tw = turn_mine;
+        tpar = need & 1;
+      }
+    }
     bool ok;
     if (need_mask)
       ok = fwd_softmax_block<Cfg, BF16, SOFTCAP, true>(c, p, s_addr, o_addr, o_full, p_full, n, lo_key - j * BN,
-                                                       hi_key - j * BN, cmul, m, l);
+                                                       hi_key - j * BN, cmul, m, l, tw, tpar, turn_other);
     else
-      ok = fwd_softmax_block<Cfg, BF16, SOFTCAP, false>(c, p, s_addr, o_addr, o_full, p_full, n, 0, 0, cmul, m, l);
+      ok = fwd_softmax_block<Cfg, BF16, SOFTCAP, false>(c, p, s_addr, o_addr, o_full, p_full, n, 0, 0, cmul, m, l, tw,
+                                                        tpar, turn_other);
     if (!ok) return;
   }
 
@@ -444,9 +510,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   FwdCtx<Cfg, BF16> c;
   c.sQ = smem;
-  c.sK = c.sQ + NQ * Cfg::Q_TILE_BYTES;
-  c.sV = c.sK + Cfg::STAGES * Cfg::KV_STAGE_BYTES;
-  c.bars = reinterpret_cast<uint64_t*>(c.sV + Cfg::STAGES * Cfg::KV_STAGE_BYTES);
+  c.sKV = c.sQ + NQ * Cfg::Q_TILE_BYTES;
+  c.bars = reinterpret_cast<uint64_t*>(c.sKV + Cfg::SLOTS * Cfg::KV_STAGE_BYTES);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(c.bars + Cfg::NUM_BARS);
   c.abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -473,8 +538,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
     for (int i = 0; i < Cfg::NUM_BARS; ++i) {
       const bool is_p_full = (i >= Cfg::BAR_P_FULL && i < Cfg::BAR_P_FULL + NQ);               // 4 softmax warps
-      const bool is_empty = (i >= Cfg::BAR_K_EMPTY && i < Cfg::BAR_K_EMPTY + Cfg::STAGES) ||
-                            (i >= Cfg::BAR_V_EMPTY && i < Cfg::BAR_V_EMPTY + Cfg::STAGES);      // NQ MMA issuers
+      const bool is_empty = (i >= Cfg::BAR_EMPTY && i < Cfg::BAR_EMPTY + Cfg::SLOTS);           // NQ MMA issuers
       mbar_init(&c.bars[i], is_p_full ? 4u : is_empty ? (uint32_t)NQ : 1u);
     }
     *c.abort_flag = 0;

@@ -66,7 +66,8 @@ enum WaitCode : int {
   WAIT_T_EMPTY = 12,
   WAIT_N_FULL = 13,   // noise tile
   WAIT_N_EMPTY = 14,
-  WAIT_DRAIN = 15
+  WAIT_DRAIN = 15,
+  WAIT_TURN = 16      // exp-phase turn-taking between the two query tiles
 };
 
 // ---------------------------------------------------------------------------
