@@ -30,18 +30,20 @@ struct FwdParams {
   float cap_out;      // softcap * log2(e)
 };
 
-template <int D_, int BN_, int NQ_>
+// SB = S buffers per query tile in TMEM.  With SB = 2 the S tile of block j+1 is computed while the softmax of
+// block j runs, so a tile's softmax never waits for the tensor pipe in steady state.
+template <int D_, int BN_, int NQ_, int SB_>
 struct FwdCfg {
-  static constexpr int D = D_, BN = BN_, NQ = NQ_;
+  static constexpr int D = D_, BN = BN_, NQ = NQ_, SB = SB_;
   static constexpr int BM = 128;
   static constexpr int KSUB = D / 64;                 // 64-element (128-byte) column blocks of a row
   static constexpr int Q_TILE_BYTES = BM * D * 2;
   static constexpr int KV_STAGE_BYTES = BN * D * 2;
-  // one ring for K and V blocks (K(j) is item 2n, V(j) item 2n+1): as many slots as fit beside Q, at most 6
+  // one ring for K and V blocks (K(j) is item 2n, V(j) item 2n+1): as many slots as fit beside Q, at most 8
   static constexpr int SLOTS_FIT = (232448 - 2048 - NQ * Q_TILE_BYTES) / KV_STAGE_BYTES;
-  static constexpr int SLOTS = SLOTS_FIT > 6 ? 6 : SLOTS_FIT;
+  static constexpr int SLOTS = SLOTS_FIT > 8 ? 8 : SLOTS_FIT;
   static_assert(SLOTS >= 3, "ring too shallow");
-  static constexpr int O_BASE = ((NQ * BN + D - 1) / D) * D;
+  static constexpr int O_BASE = ((NQ * SB * BN + D - 1) / D) * D;
   static constexpr int TMEM_USED = O_BASE + NQ * D;
   static constexpr int TMEM_COLS = TMEM_USED <= 32 ? 32 : TMEM_USED <= 64 ? 64 : TMEM_USED <= 128 ? 128
                                    : TMEM_USED <= 256 ? 256 : 512;
@@ -51,10 +53,10 @@ struct FwdCfg {
   static constexpr bool REBALANCE_REGS = NQ == 2;
   // barrier slots
   static constexpr int BAR_Q_FULL = 0;                       // [NQ]
-  static constexpr int BAR_S_FULL = BAR_Q_FULL + NQ;         // [NQ]
-  static constexpr int BAR_P_FULL = BAR_S_FULL + NQ;         // [NQ]
-  static constexpr int BAR_O_FULL = BAR_P_FULL + NQ;         // [NQ]
-  static constexpr int BAR_FULL = BAR_O_FULL + NQ;           // [SLOTS]
+  static constexpr int BAR_S_FULL = BAR_Q_FULL + NQ;         // [NQ][SB]
+  static constexpr int BAR_P_FULL = BAR_S_FULL + NQ * SB;    // [NQ][SB]
+  static constexpr int BAR_O_FULL = BAR_P_FULL + NQ * SB;    // [NQ][2]: P V(n) completes O barrier n % 2
+  static constexpr int BAR_FULL = BAR_O_FULL + NQ * 2;       // [SLOTS]
   static constexpr int BAR_EMPTY = BAR_FULL + SLOTS;         // [SLOTS]
   static constexpr int BAR_DRAIN = BAR_EMPTY + SLOTS;        // [NQ] one drain barrier per MMA issuer
   static constexpr int BAR_TURN = BAR_DRAIN + NQ;            // [NQ][4]: exp-phase turn of softmax warp w of tile t
@@ -108,23 +110,29 @@ __device__ __forceinline__ void fwd_producer(const FwdCtx<Cfg, BF16>& c, const C
                     ks * 64, c.h, c.q0 + t * Cfg::BM, c.b);
     }
   }
-  const int items = 2 * (c.jmax - c.jmin);   // K(j) is ring item 2n, V(j) item 2n+1, n = j - jmin
+  // Ring items in the order the MMA issuers consume them: K(0..SB-1), then V(n), K(n+SB) for n = 0, 1, ...
+  const int nb = c.jmax - c.jmin;
   int issued = 0;
   bool ok = true;
-  for (int i = 0; i < items; ++i) {
-    const int slot = i % SL, use = i / SL, j = c.jmin + (i >> 1);
+  auto load = [&](bool is_v, int n) {
+    const int i = issued, slot = i % SL, use = i / SL;
     if (use > 0 && !mbar_wait(&c.bars[Cfg::BAR_EMPTY + slot], (use - 1) & 1, c.abort_flag, WAIT_K_EMPTY)) {
       ok = false;
-      break;
+      return;
     }
     uint64_t* full = &c.bars[Cfg::BAR_FULL + slot];
     uint8_t* dst = c.sKV + slot * Cfg::KV_STAGE_BYTES;
-    const CUtensorMap* tm = (i & 1) ? tm_v : tm_k;
+    const CUtensorMap* tm = is_v ? tm_v : tm_k;
     mbar_expect_tx(full, Cfg::KV_STAGE_BYTES);
 #pragma unroll
     for (int ks = 0; ks < Cfg::KSUB; ++ks)
-      tma_load_4d(dst + ks * (Cfg::BN * 128), tm, full, ks * 64, c.hk, j * Cfg::BN, c.b);
+      tma_load_4d(dst + ks * (Cfg::BN * 128), tm, full, ks * 64, c.hk, (c.jmin + n) * Cfg::BN, c.b);
     issued = i + 1;
+  };
+  for (int n = 0; n < Cfg::SB && n < nb && ok; ++n) load(false, n);
+  for (int n = 0; n < nb && ok; ++n) {
+    load(true, n);
+    if (ok && n + Cfg::SB < nb) load(false, n + Cfg::SB);
   }
   if (!ok || *c.abort_flag != 0) {
     // Abort path: do not leave the CTA while our own bulk copies may still be landing in shared memory.
@@ -153,23 +161,21 @@ __device__ __forceinline__ void fwd_producer(const FwdCtx<Cfg, BF16>& c, const C
 // a tile's visible range the arrive is immediate.
 template <class Cfg, bool BF16, int T>
 __device__ __forceinline__ void fwd_mma(const FwdCtx<Cfg, BF16>& c) {
-  constexpr int SL = Cfg::SLOTS, D = Cfg::D, BN = Cfg::BN, BM = Cfg::BM;
+  constexpr int SL = Cfg::SLOTS, D = Cfg::D, BN = Cfg::BN, BM = Cfg::BM, SB = Cfg::SB;
   constexpr uint32_t IDESC_S = make_idesc(BF16, BM, BN, false, false);
   constexpr uint32_t IDESC_PV = make_idesc(BF16, BM, D, false, true);
   // descriptor halves: the upper word is constant, the lower word is (address >> 4) plus a compile-time step
   const uint32_t desc_hi = smem_desc_hi(1024);
   const uint32_t q_lo = smem_desc_lo(smem_u32(c.sQ) + T * Cfg::Q_TILE_BYTES, 16);
   const uint32_t k_lo = smem_desc_lo(smem_u32(c.sKV), 16);
-  const uint32_t v_lo = smem_desc_lo(smem_u32(c.sKV), BN * 128);   // MN-major: LBO = bytes between 64-wide column blocks
-  const uint32_t s_tmem = c.tmem_base + T * BN;                   // S tile; P (packed 16-bit) overwrites its first half
+  const uint32_t v_lo = smem_desc_lo(smem_u32(c.sKV), BN * 128);  // MN-major: LBO = bytes between 64-wide column blocks
+  const uint32_t s_tmem0 = c.tmem_base + T * SB * BN;             // S buffers; P (packed 16-bit) overwrites the first half
   const uint32_t o_tmem = c.tmem_base + Cfg::O_BASE + T * D;
   const int lo = c.rng[T].lo, hi = c.rng[T].hi;
-  uint64_t* s_full = &c.bars[Cfg::BAR_S_FULL + T];
-  uint64_t* p_full = &c.bars[Cfg::BAR_P_FULL + T];
-  uint64_t* o_full = &c.bars[Cfg::BAR_O_FULL + T];
 
-  auto issue_s = [&](int slot) {
+  auto issue_s = [&](int slot, int buf) {
     const uint32_t b0 = k_lo + (uint32_t)(slot * (Cfg::KV_STAGE_BYTES >> 4));
+    const uint32_t s_tmem = s_tmem0 + buf * BN;
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
       const uint32_t a_off = (uint32_t)(((kk / 4) * (BM * 128) + (kk % 4) * 32) >> 4);
@@ -179,11 +185,13 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<Cfg, BF16>& c) {
       else
         umma_ss_c<IDESC_S, 1>(s_tmem, q_lo + a_off, b0 + b_off, desc_hi);
     }
-    umma_commit(s_full);
+    umma_commit(&c.bars[Cfg::BAR_S_FULL + T * SB + buf]);
   };
-  auto issue_pv = [&](int slot, bool first) {
+  auto issue_pv = [&](int slot, int buf, int nt) {
+    const bool first = nt == 0;
     const uint32_t b0 = v_lo + (uint32_t)(slot * (Cfg::KV_STAGE_BYTES >> 4));
-    // V stage: KSUB column blocks of [BN keys][64 dims]; 16 keys = 2048 bytes further down; P: 8 columns per 16 keys
+    const uint32_t s_tmem = s_tmem0 + buf * BN;
+    // V block: KSUB column blocks of [BN keys][64 dims]; 16 keys = 2048 bytes further down; P: 8 columns per 16 keys
     if (first)
       umma_ts_c<IDESC_PV, 0>(o_tmem, s_tmem, b0, desc_hi);
     else
@@ -191,62 +199,63 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<Cfg, BF16>& c) {
 #pragma unroll
     for (int kk = 1; kk < BN / 16; ++kk)
       umma_ts_c<IDESC_PV, 1>(o_tmem, s_tmem + kk * 8, b0 + (uint32_t)(kk * (2048 >> 4)), desc_hi);
-    umma_commit(o_full);
+    // Two O barriers used alternately: the softmax warps can run two blocks ahead of the P V products, and a
+    // parity wait is exact only while at most one phase of a barrier is outstanding.
+    umma_commit(&c.bars[Cfg::BAR_O_FULL + T * 2 + (nt & 1)]);
   };
 
-  // All 32 lanes walk the loop (warp-uniform), one elected lane issues.  Every ring slot is waited for (FULL)
-  // before this issuer releases it (EMPTY), also for blocks outside the tile's range: an issuer can therefore
-  // never run more than the ring depth ahead of the other one, which keeps the count-NQ EMPTY barriers
-  // phase-exact.
+  // All 32 lanes walk the loop (warp-uniform), one elected lane issues.  The issuer walks the ring items in
+  // producer order -- K(0..SB-1), then V(n), K(n+SB) -- and every slot is waited for (FULL) before this issuer
+  // releases it (EMPTY), also for blocks outside the tile's range: an issuer can therefore never run more than
+  // the ring depth ahead of the other one, which keeps the count-NQ EMPTY barriers phase-exact.
   bool ok = true;
-  if (c.jmax > c.jmin) {   // prologue: S of the first block (ring item 0)
-    ok = mbar_wait(&c.bars[Cfg::BAR_FULL + 0], 0, c.abort_flag, WAIT_K_FULL);
-    if (ok && c.jmin >= lo && c.jmin < hi) {
+  int item = 0;
+  bool q_ready = false;
+  auto k_item = [&](int n) {   // S(j) = Q K(j)^T into buffer (j - lo) % SB
+    const int j = c.jmin + n, slot = item % SL, ph = (item / SL) & 1;
+    ++item;
+    const bool act = j >= lo && j < hi;
+    if (act && !q_ready) {
       ok = mbar_wait(&c.bars[Cfg::BAR_Q_FULL + T], 0, c.abort_flag, WAIT_Q_FULL);
-      if (ok) {
-        tc_fence_after();
-        if (elect_one()) issue_s(0);
-      }
+      q_ready = true;
     }
-    if (ok && elect_one()) umma_commit(&c.bars[Cfg::BAR_EMPTY + 0]);
+    ok = ok && mbar_wait(&c.bars[Cfg::BAR_FULL + slot], ph, c.abort_flag, WAIT_K_FULL);
+    if (!ok) return;
+    tc_fence_after();
+    if (elect_one()) {
+      if (act) {
+        B200_TL((2 * 64 + (n & 63)) * 8 + T * 4 + 2);
+        issue_s(slot, (j - lo) % SB);
+        B200_TL((2 * 64 + (n & 63)) * 8 + T * 4 + 3);
+      }
+      umma_commit(&c.bars[Cfg::BAR_EMPTY + slot]);   // K(j) consumed by this tile
+    }
     __syncwarp();
-  }
-  for (int j = c.jmin; j < c.jmax && ok; ++j) {
-    const int n = j - c.jmin;
-    {  // O += P(j) V(j): ring item 2n+1
-      const int i = 2 * n + 1, slot = i % SL, ph = (i / SL) & 1;
-      const bool act = j >= lo && j < hi;
-      if (act) ok = mbar_wait(p_full, (j - lo) & 1, c.abort_flag, WAIT_P_FULL);
-      ok = ok && mbar_wait(&c.bars[Cfg::BAR_FULL + slot], ph, c.abort_flag, WAIT_V_FULL);
-      if (!ok) break;
-      tc_fence_after();
-      if (elect_one()) {
-        if (act) {
-          B200_TL((2 * 64 + (n & 63)) * 8 + T * 4 + 0);
-          issue_pv(slot, j == lo);
-          B200_TL((2 * 64 + (n & 63)) * 8 + T * 4 + 1);
-        }
-        umma_commit(&c.bars[Cfg::BAR_EMPTY + slot]);   // V(j) consumed by this tile
+  };
+  auto v_item = [&](int n) {   // O += P(j) V(j)
+    const int j = c.jmin + n, slot = item % SL, ph = (item / SL) & 1;
+    ++item;
+    const bool act = j >= lo && j < hi;
+    const int nt = j - lo, buf = nt % SB;
+    if (act) ok = mbar_wait(&c.bars[Cfg::BAR_P_FULL + T * SB + buf], (nt / SB) & 1, c.abort_flag, WAIT_P_FULL);
+    ok = ok && mbar_wait(&c.bars[Cfg::BAR_FULL + slot], ph, c.abort_flag, WAIT_V_FULL);
+    if (!ok) return;
+    tc_fence_after();
+    if (elect_one()) {
+      if (act) {
+        B200_TL((2 * 64 + (n & 63)) * 8 + T * 4 + 0);
+        issue_pv(slot, buf, nt);
+        B200_TL((2 * 64 + (n & 63)) * 8 + T * 4 + 1);
       }
-      __syncwarp();
+      umma_commit(&c.bars[Cfg::BAR_EMPTY + slot]);   // V(j) consumed by this tile
     }
-    if (j + 1 < c.jmax) {  // S(j+1) = Q K(j+1)^T: ring item 2n+2
-      const int i = 2 * n + 2, slot = i % SL, ph = (i / SL) & 1;
-      const bool act = j + 1 >= lo && j + 1 < hi;
-      if (act && j + 1 == lo) ok = mbar_wait(&c.bars[Cfg::BAR_Q_FULL + T], 0, c.abort_flag, WAIT_Q_FULL);
-      ok = ok && mbar_wait(&c.bars[Cfg::BAR_FULL + slot], ph, c.abort_flag, WAIT_K_FULL);
-      if (!ok) break;
-      tc_fence_after();
-      if (elect_one()) {
-        if (act) {
-          B200_TL((2 * 64 + ((n + 1) & 63)) * 8 + T * 4 + 2);
-          issue_s(slot);
-          B200_TL((2 * 64 + ((n + 1) & 63)) * 8 + T * 4 + 3);
-        }
-        umma_commit(&c.bars[Cfg::BAR_EMPTY + slot]);  // K(j+1) consumed by this tile
-      }
-      __syncwarp();
-    }
+    __syncwarp();
+  };
+  const int nb = c.jmax - c.jmin;
+  for (int n = 0; n < SB && n < nb && ok; ++n) k_item(n);
+  for (int n = 0; n < nb && ok; ++n) {
+    v_item(n);
+    if (ok && n + SB < nb) k_item(n + SB);
   }
   // every MMA issued above has retired before the CTA tears TMEM down
   if (elect_one()) umma_commit(&c.bars[Cfg::BAR_DRAIN + T]);
@@ -277,6 +286,13 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
   return out;
 }
 
+// head_dim 128 tiling: key block width and S buffers per query tile (64 x 2 double-buffers S in TMEM)
+#ifndef B200_BN128
+#define B200_BN128 64
+#endif
+#ifndef B200_SB128
+#define B200_SB128 2
+#endif
 #ifndef B200_POLY_OF_8
 #define B200_POLY_OF_8 0
 #endif
@@ -341,7 +357,10 @@ __device__ __forceinline__ bool fwd_softmax_block(const FwdCtx<Cfg, BF16>& c, co
     rescale = true;
   }
   if (n > 0 && __any_sync(0xffffffffu, rescale)) {
-    if (!mbar_wait(o_full, (n - 1) & 1, c.abort_flag, WAIT_O_FULL)) return false;
+    // P V(n-1): barrier (n-1) % 2, phase (n-1) / 2.  S(n) has completed, hence every earlier MMA of this tile up to
+    // P V(n-2) too, and P V(n+1) cannot start before this thread delivers P(n): the barrier is exactly in or
+    // just past the awaited phase.
+    if (!mbar_wait(o_full + ((n - 1) & 1), ((n - 1) >> 1) & 1, c.abort_flag, WAIT_O_FULL)) return false;
     tc_fence_after();
     const float2 a2 = make_float2(alpha, alpha);
 #pragma unroll
@@ -413,11 +432,10 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<Cfg, BF16>& c, const Fw
   const int r_tile = c.q0 + t * Cfg::BM;
   const int row = r_tile + warp_q * 32 + lane;
   const uint32_t lane_addr = c.tmem_base + ((uint32_t)(warp_q * 32) << 16);
-  const uint32_t s_addr = lane_addr + t * BN;
+  constexpr int SB = Cfg::SB;
+  const uint32_t s_addr0 = lane_addr + t * SB * BN;
   const uint32_t o_addr = lane_addr + Cfg::O_BASE + t * D;
-  uint64_t* s_full = &c.bars[Cfg::BAR_S_FULL + t];
-  uint64_t* p_full = &c.bars[Cfg::BAR_P_FULL + t];
-  uint64_t* o_full = &c.bars[Cfg::BAR_O_FULL + t];
+  uint64_t* o_full = &c.bars[Cfg::BAR_O_FULL + t * 2];   // [2], P V(n) completes o_full[n % 2], phase n / 2
 
   const float cmul = SOFTCAP ? p.cap_out : p.scale_log2;
   float m = -1.0e30f;  // running reference maximum (base-2 units); finite so that fully masked blocks stay NaN-free
@@ -441,8 +459,10 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<Cfg, BF16>& c, const Fw
   }
 
   for (int j = rng.lo; j < rng.hi; ++j) {
-    const int n = j - rng.lo;
-    if (!mbar_wait(s_full, n & 1, c.abort_flag, WAIT_S_FULL)) return;
+    const int n = j - rng.lo, buf = n % SB;
+    const uint32_t s_addr = s_addr0 + buf * BN;
+    uint64_t* p_full = &c.bars[Cfg::BAR_P_FULL + t * SB + buf];
+    if (!mbar_wait(&c.bars[Cfg::BAR_S_FULL + t * SB + buf], (n / SB) & 1, c.abort_flag, WAIT_S_FULL)) return;
     tc_fence_after();
     // a block needs element masks only if some row of the tile sees it partially
     const bool need_mask = (hi_first - j * BN < BN - 1) || (lo_last - j * BN > 0);
@@ -466,7 +486,8 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<Cfg, BF16>& c, const Fw
   }
 
   // epilogue: O / l -> 16-bit -> global (BSHD), base-2 LSE for the score passes
-  if (!mbar_wait(o_full, (rng.hi - rng.lo - 1) & 1, c.abort_flag, WAIT_O_FULL)) return;
+  const int last = rng.hi - rng.lo - 1;
+  if (!mbar_wait(o_full + (last & 1), (last >> 1) & 1, c.abort_flag, WAIT_O_FULL)) return;
   tc_fence_after();
   const float inv_l = 1.0f / l;
   const bool in_range = row < p.q_len;
@@ -493,11 +514,11 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<Cfg, BF16>& c, const Fw
 }
 
 // ----------------------------------- kernel ----------------------------------
-template <int D, int BN, int NQ, bool BF16, bool SOFTCAP>
-__global__ void __launch_bounds__(FwdCfg<D, BN, NQ>::THREADS, 1)
+template <int D, int BN, int NQ, int SB, bool BF16, bool SOFTCAP>
+__global__ void __launch_bounds__(FwdCfg<D, BN, NQ, SB>::THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
-  using Cfg = FwdCfg<D, BN, NQ>;
+  using Cfg = FwdCfg<D, BN, NQ, SB>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
@@ -537,7 +558,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (threadIdx.x == 0) {
 #pragma unroll
     for (int i = 0; i < Cfg::NUM_BARS; ++i) {
-      const bool is_p_full = (i >= Cfg::BAR_P_FULL && i < Cfg::BAR_P_FULL + NQ);               // 4 softmax warps
+      const bool is_p_full = (i >= Cfg::BAR_P_FULL && i < Cfg::BAR_P_FULL + NQ * SB);          // 4 softmax warps
       const bool is_empty = (i >= Cfg::BAR_EMPTY && i < Cfg::BAR_EMPTY + Cfg::SLOTS);           // NQ MMA issuers
       mbar_init(&c.bars[i], is_p_full ? 4u : is_empty ? (uint32_t)NQ : 1u);
     }
@@ -586,11 +607,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }
 
 // --------------------------------- host side ---------------------------------
-template <int D, int BN, int NQ, bool BF16, bool SOFTCAP>
+template <int D, int BN, int NQ, int SB, bool BF16, bool SOFTCAP>
 int launch_attn_fwd_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
                         cudaStream_t stream) {
-  using Cfg = FwdCfg<D, BN, NQ>;
-  auto kern = attn_fwd_kernel<D, BN, NQ, BF16, SOFTCAP>;
+  using Cfg = FwdCfg<D, BN, NQ, SB>;
+  auto kern = attn_fwd_kernel<D, BN, NQ, SB, BF16, SOFTCAP>;
   static thread_local int configured_dev = -1;
   int dev = 0;
   B200_CUDA_TRY(cudaGetDevice(&dev));
@@ -621,7 +642,7 @@ inline int attn_fwd_impl_lse_stride(const void* q, const void* k, const void* v,
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return B200_ERR_MISALIGNED;
 
   const bool bf16 = dtype == B200_BF16;
-  const int bn = head_dim == 128 ? 128 : 64;
+  const int bn = head_dim == 128 ? B200_BN128 : 64;
   CUtensorMap tq, tk, tv;
   int rc;
   if ((rc = make_bshd_tensor_map(&tq, q, batch, q_len, heads, head_dim, 128, bf16)) != B200_OK) return rc;
@@ -646,18 +667,17 @@ inline int attn_fwd_impl_lse_stride(const void* q, const void* k, const void* v,
   p.cap_out = softcap * kLog2e;
   const bool cap = softcap > 0.f;
 
-#define B200_FWD_DISPATCH(D_, BN_, NQ_)                                                                      \
-  (bf16 ? (cap ? launch_attn_fwd_cfg<D_, BN_, NQ_, true, true>(tq, tk, tv, p, stream)                        \
-               : launch_attn_fwd_cfg<D_, BN_, NQ_, true, false>(tq, tk, tv, p, stream))                      \
-        : (cap ? launch_attn_fwd_cfg<D_, BN_, NQ_, false, true>(tq, tk, tv, p, stream)                       \
-               : launch_attn_fwd_cfg<D_, BN_, NQ_, false, false>(tq, tk, tv, p, stream)))
+#define B200_FWD_DISPATCH(D_, BN_, NQ_, SB_)                                                                 \
+  (bf16 ? (cap ? launch_attn_fwd_cfg<D_, BN_, NQ_, SB_, true, true>(tq, tk, tv, p, stream)                   \
+               : launch_attn_fwd_cfg<D_, BN_, NQ_, SB_, true, false>(tq, tk, tv, p, stream))                 \
+        : (cap ? launch_attn_fwd_cfg<D_, BN_, NQ_, SB_, false, true>(tq, tk, tv, p, stream)                  \
+               : launch_attn_fwd_cfg<D_, BN_, NQ_, SB_, false, false>(tq, tk, tv, p, stream)))
   if (head_dim == 128) {
-    // two query tiles per CTA keep the tensor pipe busy while one tile is in its softmax;
-    // short sequences use one tile per CTA so that more CTAs exist
-    if (q_len > 128) return B200_FWD_DISPATCH(128, 128, 2);
-    return B200_FWD_DISPATCH(128, 128, 1);
+    // two query tiles per CTA; short sequences use one tile per CTA so that more CTAs exist
+    if (q_len > 128) return B200_FWD_DISPATCH(128, B200_BN128, 2, B200_SB128);
+    return B200_FWD_DISPATCH(128, B200_BN128, 1, B200_SB128);
   }
-  return B200_FWD_DISPATCH(256, 64, 1);
+  return B200_FWD_DISPATCH(256, 64, 1, 2);
 #undef B200_FWD_DISPATCH
 }
 
