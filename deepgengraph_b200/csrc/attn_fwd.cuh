@@ -215,6 +215,7 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<Cfg, BF16>& c) {
     const int j = c.jmin + n, slot = item % SL, ph = (item / SL) & 1;
     ++item;
     const bool act = j >= lo && j < hi;
+    if (elect_one()) B200_TL((3 * 64 + (n & 63)) * 8 + T * 4 + 2);
     if (act && !q_ready) {
       ok = mbar_wait(&c.bars[Cfg::BAR_Q_FULL + T], 0, c.abort_flag, WAIT_Q_FULL);
       q_ready = true;
@@ -223,6 +224,7 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<Cfg, BF16>& c) {
     if (!ok) return;
     tc_fence_after();
     if (elect_one()) {
+      B200_TL((3 * 64 + (n & 63)) * 8 + T * 4 + 3);
       if (act) {
         B200_TL((2 * 64 + (n & 63)) * 8 + T * 4 + 2);
         issue_s(slot, (j - lo) % SB);
@@ -237,7 +239,9 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<Cfg, BF16>& c) {
     ++item;
     const bool act = j >= lo && j < hi;
     const int nt = j - lo, buf = nt % SB;
+    if (elect_one()) B200_TL((3 * 64 + (n & 63)) * 8 + T * 4 + 0);
     if (act) ok = mbar_wait(&c.bars[Cfg::BAR_P_FULL + T * SB + buf], (nt / SB) & 1, c.abort_flag, WAIT_P_FULL);
+    if (elect_one()) B200_TL((3 * 64 + (n & 63)) * 8 + T * 4 + 1);
     ok = ok && mbar_wait(&c.bars[Cfg::BAR_FULL + slot], ph, c.abort_flag, WAIT_V_FULL);
     if (!ok) return;
     tc_fence_after();
@@ -528,6 +532,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(&g_device_status);
   __syncthreads();
   if (s_skip != 0) return;
+  B200_TL_INIT();
 
   FwdCtx<Cfg, BF16> c;
   c.sQ = smem;

@@ -41,12 +41,21 @@ __device__ int g_device_status = 0;
 #ifdef B200_TIMELINE
 __device__ long long* g_timeline = nullptr;
 __device__ int g_timeline_block = 0;
-#define B200_TL(slot)                                                                                  \
-  do {                                                                                                 \
-    if (g_timeline != nullptr && (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) == g_timeline_block) \
-      g_timeline[(slot)] = clock64();                                                                  \
+__shared__ long long* s_timeline;   // per CTA: the buffer if this CTA is the selected one, else null
+#define B200_TL_INIT()                                                                                   \
+  do {                                                                                                   \
+    if (threadIdx.x == 0)                                                                                \
+      s_timeline = ((int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) == g_timeline_block) \
+                       ? g_timeline : nullptr;                                                           \
+    __syncthreads();                                                                                     \
+  } while (0)
+#define B200_TL(slot)                                  \
+  do {                                                 \
+    long long* _tl = s_timeline;                       \
+    if (_tl != nullptr) _tl[(slot)] = clock64();       \
   } while (0)
 #else
+#define B200_TL_INIT() do { } while (0)
 #define B200_TL(slot) do { } while (0)
 #endif
 
