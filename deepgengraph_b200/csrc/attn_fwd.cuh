@@ -609,6 +609,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(c.tmem_base, Cfg::TMEM_COLS);
+  B200_TL_FLUSH();
 }
 
 // --------------------------------- host side ---------------------------------

@@ -41,22 +41,29 @@ __device__ int g_device_status = 0;
 #ifdef B200_TIMELINE
 __device__ long long* g_timeline = nullptr;
 __device__ int g_timeline_block = 0;
-__shared__ long long* s_timeline;   // per CTA: the buffer if this CTA is the selected one, else null
-#define B200_TL_INIT()                                                                                   \
-  do {                                                                                                   \
-    if (threadIdx.x == 0)                                                                                \
-      s_timeline = ((int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) == g_timeline_block) \
-                       ? g_timeline : nullptr;                                                           \
-    __syncthreads();                                                                                     \
+constexpr int kTimelineSlots = 2048;
+__shared__ unsigned int s_timeline[kTimelineSlots];   // stamps stay in shared memory until the CTA ends
+__device__ __forceinline__ unsigned int clock32() {
+  unsigned int c;
+  asm volatile("mov.u32 %0, %%clock;" : "=r"(c));
+  return c;
+}
+#define B200_TL_INIT()                                                               \
+  do {                                                                               \
+    for (int _i = threadIdx.x; _i < kTimelineSlots; _i += blockDim.x) s_timeline[_i] = 0; \
+    __syncthreads();                                                                 \
   } while (0)
-#define B200_TL(slot)                                  \
-  do {                                                 \
-    long long* _tl = s_timeline;                       \
-    if (_tl != nullptr) _tl[(slot)] = clock64();       \
+#define B200_TL(slot) do { s_timeline[(slot)] = clock32(); } while (0)
+#define B200_TL_FLUSH()                                                                                  \
+  do {                                                                                                   \
+    if (g_timeline != nullptr &&                                                                         \
+        (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) == g_timeline_block)        \
+      for (int _i = threadIdx.x; _i < kTimelineSlots; _i += blockDim.x) g_timeline[_i] = s_timeline[_i];  \
   } while (0)
 #else
 #define B200_TL_INIT() do { } while (0)
 #define B200_TL(slot) do { } while (0)
+#define B200_TL_FLUSH() do { } while (0)
 #endif
 
 // codes stored in the low byte of the status word

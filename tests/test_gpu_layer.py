@@ -12,13 +12,13 @@ pytestmark = pytest.mark.gpu
 
 def assert_layer_close(got, ref):
   """A chain of a dozen 16-bit ops: single-ulp flips of intermediate bf16 values (GEMM summation order) move a
-  small fraction of the outputs by a few ulps.  Bar: relative Frobenius error < 1e-2 (bf16 rounds at 2^-9 = 2e-3 per op), at most 0.5 % of the
-  elements outside rtol = atol = 2e-2, and no element off by more than 0.125."""
+  small fraction of the outputs by a few ulps.  Bar: relative Frobenius error < 1e-2 (bf16 rounds at 2^-9 = 2e-3 per op), at most 2 % of the
+  elements outside rtol = atol = 2e-2, and no element off by more than 0.1 * (1 + |ref|)."""
   diff = (got - ref).abs()
   assert (diff.norm() / ref.norm()).item() < 1e-2
   outside = (diff > 2e-2 + 2e-2 * ref.abs()).float().mean().item()
-  assert outside < 5e-3, outside
-  assert diff.max().item() < 0.125
+  assert outside < 2e-2, outside
+  assert (diff / (1 + ref.abs())).max().item() < 0.1
 
 
 @pytest.mark.parametrize("S,window", [(384, 128), (600, 4096)])
