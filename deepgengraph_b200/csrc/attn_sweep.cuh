@@ -433,6 +433,10 @@ score_reduce_kernel(float* __restrict__ out, float* __restrict__ out_sq, const f
 }
 
 // --------------------------------- host side ---------------------------------
+// size of the library's built-in scratch for b200_attn_score_static (32 MiB per GPU that loads the library)
+constexpr int64_t kStaticScoreScratchBytes = 32ll << 20;
+int static_score_scratch(void** out);
+
 constexpr int kSweepChunkBlocks = 8;   // streamed blocks per CTA in the column-sum sweeps
 
 struct ScoreWorkspace {

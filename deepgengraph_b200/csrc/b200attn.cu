@@ -3,6 +3,7 @@
 #include <algorithm>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 #include "elementwise.cuh"
@@ -61,6 +62,32 @@ int make_f32_matrix_tensor_map(CUtensorMap* map, const void* base, int64_t rows,
     g_last_cuda_error = (int)r;
     return B200_ERR_CUDA;
   }
+  return B200_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Built-in scratch of b200_attn_score_static: a fixed array in the library's device image, so that callers
+// which must not allocate device memory still have somewhere to put the row normalisers and partial sums.
+// In host code the array's NAME is only a stand-in for the symbol, not a device address; the address is looked
+// up once per device (with that device current) through cudaGetSymbolAddress and cached.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_score_scratch[kStaticScoreScratchBytes];
+
+int static_score_scratch(void** out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static void* cached[kMaxDevices] = {};
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return B200_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    B200_CUDA_TRY(cudaGetSymbolAddress(&p, g_score_scratch));
+    if (p == nullptr) return B200_ERR_CUDA;
+    cached[dev] = p;
+  }
+  *out = cached[dev];
   return B200_OK;
 }
 
@@ -202,6 +229,19 @@ int b200_attn_kf_score(const void* q, const void* k, const void* v, const float*
                        int heads, int head_dim, int dtype, int causal, float tau, float scale, void* stream) {
   return attn_kf_impl(q, k, v, exp_rand, out, kf_score, workspace, workspace_bytes, batch, q_len, kv_len, heads,
                       head_dim, dtype, causal, tau, scale, (cudaStream_t)stream);
+}
+
+int b200_attn_score_static(const void* q, const void* k, const void* v, void* out, float* score, float* score_sq,
+                           int batch, int q_len, int kv_len, int heads, int head_dim, int dtype, int causal,
+                           int window, float softcap, float scale, void* stream) {
+  const int64_t need = score_workspace_bytes(batch, q_len, kv_len, heads);
+  if (need <= 0) return B200_ERR_BAD_ARGUMENT;
+  if (need > kStaticScoreScratchBytes) return B200_ERR_WORKSPACE;   // problem too large for the built-in scratch
+  void* scratch = nullptr;
+  const int rc = static_score_scratch(&scratch);
+  if (rc != B200_OK) return rc;
+  return attn_score_impl(q, k, v, out, score, score_sq, scratch, kStaticScoreScratchBytes, batch, q_len, kv_len,
+                         heads, head_dim, dtype, causal, window, softcap, scale, (cudaStream_t)stream);
 }
 
 #ifdef B200_TIMELINE

@@ -126,6 +126,29 @@ int b200_attn_score(const void* q, const void* k, const void* v, void* out, floa
                     int window, float softcap, float scale, void* stream);
 
 /*
+ * b200_attn_score without a caller-provided workspace and without any device allocation.
+ * (No counterpart in the reference project: its generated launchers allocate freely through PyTorch.)
+ *
+ * For callers that are not allowed to call cudaMalloc -- a plugin whose host forbids allocation after
+ * start-up, code that runs where the allocator may not be entered, a process whose device memory is already
+ * fully committed -- the library carries its own scratch: a fixed 32 MiB array in its
+ * device image (every GPU that loads the library holds those 32 MiB until the process exits).  Inputs and
+ * outputs are still the caller's.  Semantics and results are those of b200_attn_score.
+ *
+ *  - Limit: b200_attn_score_workspace_bytes(batch, q_len, kv_len, heads) must not exceed 33554432 bytes
+ *    (BASELINE config 3, batch 2 x 32 heads x 4096, needs 18.9 MB); larger problems return
+ *    B200_ERR_WORKSPACE and launch nothing.
+ *  - The first call on each device looks up the scratch address (cudaGetSymbolAddress, with that device
+ *    current) and caches it; make that first call outside of any stream capture.
+ *  - All calls on a device share the one array, which keeps the previous call's contents.  Nothing in it has
+ *    to start at zero (every element that is read is written earlier in the same call), but two calls that
+ *    overlap on the GPU (for example on different streams) race on it: serialise them.
+ */
+int b200_attn_score_static(const void* q, const void* k, const void* v, void* out, float* score,
+                           float* score_sq, int batch, int q_len, int kv_len, int heads, int head_dim,
+                           int dtype, int causal, int window, float softcap, float scale, void* stream);
+
+/*
  * KeyFormer: attention output plus
  *   kf_score[b, h, j] = sum_i softmax_j((logit_ij - log(exp_rand_ij)) / tau)
  *   -- KeyFormer.forward kernels/kf.py:19-42
