@@ -316,8 +316,8 @@ __device__ __forceinline__ bool fwd_softmax_block(const FwdCtx<Cfg, BF16>& c, co
                                                   uint64_t* turn_wait, int turn_parity, uint64_t* turn_pass) {
   constexpr int D = Cfg::D, BN = Cfg::BN;
   const int lane = threadIdx.x & 31;
-  const int tl_base = (((int)(threadIdx.x >> 7)) * 64 + (n & 63)) * 8;
-  const bool tl_on = (threadIdx.x & 127) == 0;
+  [[maybe_unused]] const int tl_base = (((int)(threadIdx.x >> 7)) * 64 + (n & 63)) * 8;
+  [[maybe_unused]] const bool tl_on = (threadIdx.x & 127) == 0;
   if (tl_on) B200_TL(tl_base + 0);
   uint32_t sr[BN / 32][32];
 #pragma unroll

@@ -154,11 +154,14 @@ __device__ __forceinline__ void sweep_producer(const SweepCtx<Cfg>& c, const Swe
 }
 
 // -------------------------------- MMA issuer --------------------------------
+// All 32 lanes walk the loop (warp-uniform control flow keeps the descriptor arithmetic on the uniform
+// datapath); one elected lane issues.
 template <class Cfg, bool BF16>
 __device__ __forceinline__ void sweep_mma(const SweepCtx<Cfg>& c) {
   constexpr int ST = Cfg::STAGES, BX = Cfg::BX;
   constexpr uint32_t IDESC = make_idesc(BF16, 128, BX, false, false);
-  const uint32_t a_addr = smem_u32(c.sA), x_addr = smem_u32(c.sX);
+  const uint32_t desc_hi = smem_desc_hi(1024);
+  const uint32_t a_lo = smem_desc_lo(smem_u32(c.sA), 16), x_lo = smem_desc_lo(smem_u32(c.sX), 16);
   bool ok = mbar_wait(&c.bars[Cfg::BAR_A_FULL], 0, c.abort_flag, WAIT_Q_FULL);
   for (int blk = c.blk_lo; blk < c.blk_hi && ok; ++blk) {
     const int n = blk - c.blk_lo, st = n % ST, tb = n & 1, tuse = n >> 1;
@@ -166,16 +169,25 @@ __device__ __forceinline__ void sweep_mma(const SweepCtx<Cfg>& c) {
     ok = ok && mbar_wait(&c.bars[Cfg::BAR_X_FULL + st], (n / ST) & 1, c.abort_flag, WAIT_X_FULL);
     if (!ok) break;
     tc_fence_after();
+    if (elect_one()) {
+      const uint32_t b0 = x_lo + (uint32_t)(st * (Cfg::X_STAGE_BYTES >> 4));
+      const uint32_t d_tmem = c.tmem_base + tb * BX;
 #pragma unroll
-    for (int kk = 0; kk < 8; ++kk) {
-      const uint64_t a = make_smem_desc(a_addr + (kk / 4) * (128 * 128) + (kk % 4) * 32, 16, 1024);
-      const uint64_t bd = make_smem_desc(x_addr + st * Cfg::X_STAGE_BYTES + (kk / 4) * (BX * 128) + (kk % 4) * 32, 16, 1024);
-      umma_ss(c.tmem_base + tb * BX, a, bd, IDESC, kk > 0 ? 1u : 0u);
+      for (int kk = 0; kk < 8; ++kk) {
+        const uint32_t a_off = (uint32_t)(((kk / 4) * (128 * 128) + (kk % 4) * 32) >> 4);
+        const uint32_t b_off = (uint32_t)(((kk / 4) * (BX * 128) + (kk % 4) * 32) >> 4);
+        if (kk == 0)
+          umma_ss_c<IDESC, 0>(d_tmem, a_lo + a_off, b0 + b_off, desc_hi);
+        else
+          umma_ss_c<IDESC, 1>(d_tmem, a_lo + a_off, b0 + b_off, desc_hi);
+      }
+      umma_commit(&c.bars[Cfg::BAR_T_FULL + tb]);
+      umma_commit(&c.bars[Cfg::BAR_X_EMPTY + st]);
     }
-    umma_commit(&c.bars[Cfg::BAR_T_FULL + tb]);
-    umma_commit(&c.bars[Cfg::BAR_X_EMPTY + st]);
+    __syncwarp();
   }
-  umma_commit(&c.bars[Cfg::BAR_DRAIN]);
+  if (elect_one()) umma_commit(&c.bars[Cfg::BAR_DRAIN]);
+  __syncwarp();
   mbar_wait(&c.bars[Cfg::BAR_DRAIN], 0, c.abort_flag, WAIT_DRAIN);
 }
 
@@ -406,7 +418,7 @@ attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   } else if (warp == 4) {
     if (lane == 0) sweep_producer<Cfg>(c, p, &tm_a, &tm_x, &tm_n);
   } else {
-    if (lane == 0) sweep_mma<Cfg, BF16>(c);
+    sweep_mma<Cfg, BF16>(c);
   }
   tc_fence_before();
   __syncthreads();

@@ -84,56 +84,89 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // ---------------------------------------------------------------------------
 // RMSNorm.  out = T(x * rsqrt(mean(x^2) + eps)) * w, the last product taken in T
 // exactly as the reference does (csrc/norm.cu:54).
-// One block per row at a time, the row kept in registers: MAXV 16-byte vectors
-// per thread.  FUSED_ADD: x = input + residual, residual <- T(x), and the second
+// One warp per row, the row kept in registers: MAXV 16-byte vectors per lane.  FUSED_ADD: x = input + residual, residual <- T(x), and the second
 // phase re-reads the ROUNDED residual like csrc/norm.cu:80 (variance from the
 // unrounded sum, csrc/norm.cu:68-70).
 // ---------------------------------------------------------------------------
-template <typename T, int THREADS, int MAXV, bool FUSED_ADD>
-__global__ void __launch_bounds__(THREADS)
+template <typename T, int MAXV, bool FUSED_ADD>
+__global__ void __launch_bounds__(256)
 rms_norm_rows_kernel(T* __restrict__ out, T* __restrict__ input, T* __restrict__ residual,
                      const T* __restrict__ weight, float epsilon, int64_t num_tokens, int hidden) {
+  // One WARP per row: the row lives in the warp's registers as raw 16-byte vectors (lane l holds vectors
+  // l, l + 32, ...), the reduction is five shuffles, and no block-wide barrier sits between a row's load and
+  // its store -- every warp of the grid streams rows independently.
   constexpr int VN = 16 / sizeof(T);
-  __shared__ float red[33];
   const int nvec = hidden / VN;  // hidden % VN == 0 checked on the host
-  for (int64_t row = blockIdx.x; row < num_tokens; row += gridDim.x) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp_global = (int64_t)blockIdx.x * (256 / 32) + (threadIdx.x >> 5);
+  const int64_t warp_count = (int64_t)gridDim.x * (256 / 32);
+  for (int64_t row = warp_global; row < num_tokens; row += warp_count) {
     T* in_row = input + row * hidden;
-    float x[MAXV][VN];
+    uint4 raw[MAXV];
     float ss = 0.f;
+    if constexpr (FUSED_ADD) {
+      T* res_row = residual + row * hidden;
+      // all loads of the row are issued before the first store (a store in between would order the later loads
+      // behind it); for the widest rows the residual is consumed in two halves to stay within the register file
+      constexpr int HV = MAXV > 16 ? MAXV / 2 : MAXV;
 #pragma unroll
-    for (int v = 0; v < MAXV; ++v) {
-      const int idx = threadIdx.x + v * THREADS;
-      if (idx < nvec) {
-        unpack16<T>(FUSED_ADD ? ld_16(in_row + (int64_t)idx * VN) : ld_nc_16(in_row + (int64_t)idx * VN), x[v]);
-        if constexpr (FUSED_ADD) {
-          float r[VN];
-          T* res_row = residual + row * hidden;
-          unpack16<T>(ld_16(res_row + (int64_t)idx * VN), r);
+      for (int v = 0; v < MAXV; ++v) {
+        const int idx = lane + v * 32;
+        if (idx < nvec) raw[v] = ld_16(in_row + (int64_t)idx * VN);
+      }
 #pragma unroll
-          for (int i = 0; i < VN; ++i) {
-            x[v][i] += r[i];
-            ss += x[v][i] * x[v][i];
+      for (int h0 = 0; h0 < MAXV; h0 += HV) {
+        uint4 rres[HV];
+#pragma unroll
+        for (int v = 0; v < HV; ++v) {
+          const int idx = lane + (h0 + v) * 32;
+          if (idx < nvec) rres[v] = ld_16(res_row + (int64_t)idx * VN);
+        }
+#pragma unroll
+        for (int v = 0; v < HV; ++v) {
+          const int idx = lane + (h0 + v) * 32;
+          if (idx < nvec) {
+            float x[VN], r[VN];
+            unpack16<T>(raw[h0 + v], x);
+            unpack16<T>(rres[v], r);
+#pragma unroll
+            for (int i = 0; i < VN; ++i) {
+              x[i] += r[i];
+              ss += x[i] * x[i];      // variance from the unrounded sum (csrc/norm.cu:68-70)
+            }
+            raw[h0 + v] = pack16<T>(x);    // phase two sees the rounded residual (csrc/norm.cu:80)
+            st_16(res_row + (int64_t)idx * VN, raw[h0 + v]);
           }
-          const uint4 rounded = pack16<T>(x[v]);
-          st_16(res_row + (int64_t)idx * VN, rounded);
-          unpack16<T>(rounded, x[v]);  // phase two sees the rounded residual
-        } else {
+        }
+      }
+    } else {
 #pragma unroll
-          for (int i = 0; i < VN; ++i) ss += x[v][i] * x[v][i];
+      for (int v = 0; v < MAXV; ++v) {
+        const int idx = lane + v * 32;
+        if (idx < nvec) raw[v] = ld_nc_16(in_row + (int64_t)idx * VN);
+      }
+#pragma unroll
+      for (int v = 0; v < MAXV; ++v) {
+        const int idx = lane + v * 32;
+        if (idx < nvec) {
+          float x[VN];
+          unpack16<T>(raw[v], x);
+#pragma unroll
+          for (int i = 0; i < VN; ++i) ss += x[i] * x[i];
         }
       }
     }
-    const float total = block_sum<THREADS>(ss, red);
-    const float inv = rsqrtf(total / (float)hidden + epsilon);
+    const float inv = rsqrtf(warp_sum(ss) / (float)hidden + epsilon);
     T* out_row = (FUSED_ADD ? input : out) + row * hidden;
 #pragma unroll
     for (int v = 0; v < MAXV; ++v) {
-      const int idx = threadIdx.x + v * THREADS;
+      const int idx = lane + v * 32;
       if (idx < nvec) {
-        float w[VN], y[VN];
+        float x[VN], w[VN], y[VN];
+        unpack16<T>(raw[v], x);
         unpack16<T>(ld_16(weight + (int64_t)idx * VN), w);
 #pragma unroll
-        for (int i = 0; i < VN; ++i) y[i] = to_f32<T>(from_f32<T>(x[v][i] * inv)) * w[i];
+        for (int i = 0; i < VN; ++i) y[i] = to_f32<T>(from_f32<T>(x[i] * inv)) * w[i];
         st_16(out_row + (int64_t)idx * VN, pack16<T>(y));
       }
     }
@@ -181,15 +214,17 @@ int launch_rms_norm(void* out, void* input, void* residual, const void* weight, 
   T* in = (T*)input;
   T* res = (T*)residual;
   const T* w = (const T*)weight;
-  if (vec_ok && nvec <= 256 * 4) {
-    // 8 resident blocks of 256 threads per SM keep ~28 KB of loads in flight per SM
-    const int grid = (int)std::min<int64_t>(num_tokens, (int64_t)sms * 8);
-    if (nvec <= 256)
-      rms_norm_rows_kernel<T, 256, 1, FUSED_ADD><<<grid, 256, 0, stream>>>(o, in, res, w, eps, num_tokens, hidden);
-    else if (nvec <= 512)
-      rms_norm_rows_kernel<T, 256, 2, FUSED_ADD><<<grid, 256, 0, stream>>>(o, in, res, w, eps, num_tokens, hidden);
-    else
-      rms_norm_rows_kernel<T, 256, 4, FUSED_ADD><<<grid, 256, 0, stream>>>(o, in, res, w, eps, num_tokens, hidden);
+  if (vec_ok && nvec <= 32 * 32) {
+    // 8 rows (warps) per block; enough blocks to give every SM several resident warps per scheduler
+    const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((num_tokens + 7) / 8, (int64_t)sms * 8));
+#define B200_RMS_LAUNCH(MAXV_) \
+  rms_norm_rows_kernel<T, MAXV_, FUSED_ADD><<<grid, 256, 0, stream>>>(o, in, res, w, eps, num_tokens, hidden)
+    if (nvec <= 64) B200_RMS_LAUNCH(2);
+    else if (nvec <= 128) B200_RMS_LAUNCH(4);
+    else if (nvec <= 256) B200_RMS_LAUNCH(8);
+    else if (nvec <= 512) B200_RMS_LAUNCH(16);
+    else B200_RMS_LAUNCH(32);
+#undef B200_RMS_LAUNCH
   } else {
     const int grid = (int)std::min<int64_t>(num_tokens, (int64_t)sms * 8);
     rms_norm_generic_kernel<T, FUSED_ADD><<<grid, 256, 0, stream>>>(o, in, res, w, eps, num_tokens, hidden);
@@ -269,7 +304,7 @@ int launch_act_and_mul(void* out, const void* in, int64_t num_tokens, int d, cud
 
 // ---------------------------------------------------------------------------
 // Online rotary embedding (NeoX pairing: element i rotates with element i + D/2),
-// csrc/pos_encoding.cu:83-111.  One block per token (grid-stride); the D/2 angles
+// csrc/pos_encoding.cu:83-111.  One warp per token (grid-stride); the D/2 angles
 // are evaluated once per token with accurate powf/sincosf (the reference is built
 // with --use_fast_math; positions of several thousand radians lose most of their
 // precision there), then every head is rotated with 16-byte accesses.
@@ -279,22 +314,30 @@ __global__ void __launch_bounds__(256)
 rotary_online_kernel(const int32_t* __restrict__ positions, T* __restrict__ query, T* __restrict__ key,
                      int64_t num_tokens, int heads, int kv_heads, int64_t q_stride, int64_t k_stride,
                      float theta, int vec_ok) {
+  // One WARP per token: its D/2 angles go to a warp-private slice of shared memory (no block-wide barrier),
+  // then the warp rotates every query and key head of the token.
   constexpr int HALF = HEAD_DIM / 2;
   constexpr int VN = 16 / sizeof(T);
-  __shared__ float s_cos[HALF];
-  __shared__ float s_sin[HALF];
-  for (int64_t tok = blockIdx.x; tok < num_tokens; tok += gridDim.x) {
+  constexpr int WARPS = 256 / 32;
+  __shared__ float s_cos_all[WARPS][HALF];
+  __shared__ float s_sin_all[WARPS][HALF];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  float* s_cos = s_cos_all[wib];
+  float* s_sin = s_sin_all[wib];
+  const int64_t warp_global = (int64_t)blockIdx.x * WARPS + wib;
+  const int64_t warp_count = (int64_t)gridDim.x * WARPS;
+  for (int64_t tok = warp_global; tok < num_tokens; tok += warp_count) {
     const float pos = (float)positions[tok];
-    __syncthreads();
-    for (int i = threadIdx.x; i < HALF; i += 256) {
+    __syncwarp();
+    for (int i = lane; i < HALF; i += 32) {
       const float freq = pos / powf(theta, (float)(2 * i) / (float)HEAD_DIM);
       sincosf(freq, &s_sin[i], &s_cos[i]);
     }
-    __syncthreads();
+    __syncwarp();
     if (vec_ok) {
       constexpr int VPH = HALF / VN;  // vectors per half head
       const int total = (heads + kv_heads) * VPH;
-      for (int g = threadIdx.x; g < total; g += 256) {
+      for (int g = lane; g < total; g += 32) {
         const int head = g / VPH;
         const int c = (g - head * VPH) * VN;
         T* base = (head < heads) ? query + tok * q_stride + (int64_t)head * HEAD_DIM
@@ -313,7 +356,7 @@ rotary_online_kernel(const int32_t* __restrict__ positions, T* __restrict__ quer
       }
     } else {
       const int total = (heads + kv_heads) * HALF;
-      for (int g = threadIdx.x; g < total; g += 256) {
+      for (int g = lane; g < total; g += 32) {
         const int head = g / HALF;
         const int c = g - head * HALF;
         T* base = (head < heads) ? query + tok * q_stride + (int64_t)head * HEAD_DIM
@@ -333,7 +376,7 @@ int launch_rotary(const int32_t* positions, void* query, void* key, int64_t num_
   constexpr int VN = 16 / sizeof(T);
   const int vec_ok = aligned16(query) && aligned16(key) && (q_stride % VN == 0) && (k_stride % VN == 0) &&
                      ((head_dim / 2) % VN == 0);
-  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(num_tokens, (int64_t)sm_count() * 8));
+  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((num_tokens + 7) / 8, (int64_t)sm_count() * 8));
   T* q = (T*)query;
   T* k = (T*)key;
   switch (head_dim) {
