@@ -21,6 +21,8 @@
 // x_ij are the scaled (and soft-capped) logits in base-2 units, exactly as in the forward kernel.
 #pragma once
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "attn_fwd.cuh"
 
@@ -200,8 +202,6 @@ __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, con
   const int key = c.a0 + warp_q * 32 + lane;
   const uint32_t lane_addr = c.tmem_base + ((uint32_t)(warp_q * 32) << 16);
   const float cmul = SOFTCAP ? 1.0f : p.scale_log2;
-  float acc0 = 0.f, acc1 = 0.f, sq0 = 0.f, sq1 = 0.f;
-
   // queries visible to this key: [i_lo, i_hi]
   int i_lo = p.causal ? key - p.delta : 0;
   int i_hi = (p.causal && p.window > 0) ? min(p.q_len - 1, key + p.window - 1 - p.delta) : p.q_len - 1;
@@ -209,6 +209,47 @@ __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, con
     i_lo = 1 << 28;
     i_hi = -1;
   }
+
+  float2 acc2 = make_float2(0.f, 0.f), sq2 = make_float2(0.f, 0.f);
+  // One 32-column chunk of the tile: p = exp2(x - L_i) for the thread's key against 32 queries.
+  auto chunk_body = [&](auto mask_tag, const uint32_t (&sr)[32], int ch, const float* lse_s, const float* noise_col,
+                        int lo_c, int hi_c) {
+    constexpr bool MASK = decltype(mask_tag)::value;
+    const float2 c2 = make_float2(cmul, cmul);
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      const float4 L = *reinterpret_cast<const float4*>(lse_s + ch * 32 + i);
+      float sv[4] = {__uint_as_float(sr[i]), __uint_as_float(sr[i + 1]), __uint_as_float(sr[i + 2]),
+                     __uint_as_float(sr[i + 3])};
+      if constexpr (SOFTCAP) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) sv[u] = tanh_approx(sv[u] * p.cap_in) * p.cap_out;
+      }
+      float2 e0, e1;
+      if constexpr (KF) {
+        const float2 it2 = make_float2(p.inv_tau, p.inv_tau);
+        float g[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) g[u] = -lg2_approx(noise_col[(ch * 32 + i + u) * 32]);
+        e0 = ffma2(ffma2(make_float2(sv[0], sv[1]), c2, make_float2(g[0], g[1])), it2, make_float2(-L.x, -L.y));
+        e1 = ffma2(ffma2(make_float2(sv[2], sv[3]), c2, make_float2(g[2], g[3])), it2, make_float2(-L.z, -L.w));
+      } else {
+        e0 = ffma2(make_float2(sv[0], sv[1]), c2, make_float2(-L.x, -L.y));
+        e1 = ffma2(make_float2(sv[2], sv[3]), c2, make_float2(-L.z, -L.w));
+      }
+      float pr[4] = {ex2_approx(e0.x), ex2_approx(e0.y), ex2_approx(e1.x), ex2_approx(e1.y)};
+      if constexpr (MASK) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int col = ch * 32 + i + u;
+          if (col < lo_c || col > hi_c) pr[u] = 0.f;
+        }
+      }
+      const float2 p0 = make_float2(pr[0], pr[1]), p1 = make_float2(pr[2], pr[3]);
+      acc2 = fadd2(acc2, fadd2(p0, p1));
+      if constexpr (SQ) sq2 = ffma2(p1, p1, ffma2(p0, p0, sq2));
+    }
+  };
 
   for (int blk = c.blk_lo; blk < c.blk_hi; ++blk) {
     const int n = blk - c.blk_lo, st = n % ST, tb = n & 1;
@@ -224,40 +265,17 @@ __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, con
     const bool need_mask = (p.causal && (c.a0 + 127 - p.delta > i0)) || (i0 + BX > p.q_len) ||
                            (c.a0 + 128 > p.kv_len) ||
                            (p.causal && p.window > 0 && (c.a0 + p.window - 1 - p.delta < i0 + BX - 1));
+    // the TMEM load of chunk ch+1 is in flight while chunk ch is being reduced
+    uint32_t sr[2][32];
+    tmem_ld32(lane_addr + tb * BX, sr[0]);
 #pragma unroll
     for (int ch = 0; ch < BX / 32; ++ch) {
-      uint32_t sr[32];
-      tmem_ld32(lane_addr + tb * BX + ch * 32, sr);
       tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; i += 4) {
-        const float4 L = *reinterpret_cast<const float4*>(lse_s + ch * 32 + i);
-        const float Lv[4] = {L.x, L.y, L.z, L.w};
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          float s = __uint_as_float(sr[i + u]);
-          if constexpr (SOFTCAP) s = tanh_approx(s * p.cap_in) * p.cap_out;
-          float e;
-          if constexpr (KF) {
-            const float er = noise_col[(ch * 32 + i + u) * 32];
-            e = fmaf(fmaf(s, cmul, -lg2_approx(er)), p.inv_tau, -Lv[u]);
-          } else {
-            e = fmaf(s, cmul, -Lv[u]);
-          }
-          float pr = ex2_approx(e);
-          if (need_mask) {
-            const int col = ch * 32 + i + u;
-            if (col < lo_c || col > hi_c) pr = 0.f;
-          }
-          if (u & 1) {
-            acc1 += pr;
-            if constexpr (SQ) sq1 = fmaf(pr, pr, sq1);
-          } else {
-            acc0 += pr;
-            if constexpr (SQ) sq0 = fmaf(pr, pr, sq0);
-          }
-        }
-      }
+      if (ch + 1 < BX / 32) tmem_ld32(lane_addr + tb * BX + (ch + 1) * 32, sr[(ch + 1) & 1]);
+      if (need_mask)
+        chunk_body(std::true_type{}, sr[ch & 1], ch, lse_s, noise_col, lo_c, hi_c);
+      else
+        chunk_body(std::false_type{}, sr[ch & 1], ch, lse_s, noise_col, lo_c, hi_c);
     }
     // this TMEM buffer and this auxiliary stage may be refilled
     tc_fence_before();
@@ -267,6 +285,7 @@ __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, con
       mbar_arrive(&c.bars[Cfg::BAR_N_EMPTY + st]);
     }
   }
+  const float acc0 = acc2.x, acc1 = acc2.y, sq0 = sq2.x, sq1 = sq2.y;
   const int64_t off = ((int64_t)c.bh * p.n_chunks + chunk) * p.kv_pad + key;
   p.partial[off] = acc0 + acc1;
   if constexpr (SQ) p.partial_sq[off] = sq0 + sq1;
@@ -449,7 +468,10 @@ score_reduce_kernel(float* __restrict__ out, float* __restrict__ out_sq, const f
 constexpr int64_t kStaticScoreScratchBytes = 32ll << 20;
 int static_score_scratch(void** out);
 
-constexpr int kSweepChunkBlocks = 8;   // streamed blocks per CTA in the column-sum sweeps
+#ifndef B200_SWEEP_CHUNK
+#define B200_SWEEP_CHUNK 32
+#endif
+constexpr int kSweepChunkBlocks = B200_SWEEP_CHUNK;   // streamed blocks per CTA in the column-sum sweeps
 
 struct ScoreWorkspace {
   int lse_stride, kv_pad, n_chunks_colsum, n_chunks_kf;

@@ -136,7 +136,7 @@ int b200_attn_score(const void* q, const void* k, const void* v, void* out, floa
  * outputs are still the caller's.  Semantics and results are those of b200_attn_score.
  *
  *  - Limit: b200_attn_score_workspace_bytes(batch, q_len, kv_len, heads) must not exceed 33554432 bytes
- *    (BASELINE config 3, batch 2 x 32 heads x 4096, needs 18.9 MB); larger problems return
+ *    (batch 2 x 32 heads x seq 4096 needs 6 MiB, batch 8 needs 24 MiB); larger problems return
  *    B200_ERR_WORKSPACE and launch nothing.
  *  - The first call on each device looks up the scratch address (cudaGetSymbolAddress, with that device
  *    current) and caches it; make that first call outside of any stream capture.

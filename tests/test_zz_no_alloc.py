@@ -46,10 +46,10 @@ def test_static_scratch_entry_point_matches_workspace_entry_point(cuda_device):
 
 
 def test_static_scratch_rejects_problems_beyond_its_limit(cuda_device):
-  # batch 8 x 32 heads x 4096 needs ~75 MB of scratch: more than the built-in 32 MiB.  Nothing is launched.
-  assert _lib.load().b200_attn_score_workspace_bytes(8, 4096, 4096, 32) > 32 * 2 ** 20
+  # batch 16 x 32 heads x 4096 needs 48 MiB of scratch: more than the built-in 32 MiB.  Nothing is launched.
+  assert _lib.load().b200_attn_score_workspace_bytes(16, 4096, 4096, 32) > 32 * 2 ** 20
   dummy = torch.zeros(16, dtype=torch.bfloat16, device=cuda_device)
   st = _lib.load().b200_attn_score_static(dummy.data_ptr(), dummy.data_ptr(), dummy.data_ptr(), dummy.data_ptr(),
-                                          dummy.data_ptr(), None, 8, 4096, 4096, 32, 128, _lib.BF16, 1, 0, 0.0, 0.088,
+                                          dummy.data_ptr(), None, 16, 4096, 4096, 32, 128, _lib.BF16, 1, 0, 0.0, 0.088,
                                           None)
   assert st == 5   # B200_ERR_WORKSPACE
