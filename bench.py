@@ -32,9 +32,10 @@ sys.path.insert(0, ROOT)
 B, H, S, D = 4, 32, 4096, 128
 METRIC = "causal attn bf16 seq4k d128 TFLOP/s"
 WORKLOAD = "config2: causal MHA bf16, batch 4, 32 heads, seq 4096, head_dim 128 (per GPU)"
-# dram__bytes_read.sum + dram__bytes_write.sum of one attn_fwd_kernel launch on this workload (ncu, see
-# profiles/attn_fwd_config2.md); None until captured.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum per attn_fwd_kernel launch: ncu capture of the same kernel on 16 of
+# the 128 (batch, head) units (51.7 MB, profiles/attn_fwd_kernel_b1_h16_s4096.md) scaled by 8 -- traffic grows in
+# proportion to the units, every unit reads its q, k, v once from DRAM.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 8 * 51.7e6
 
 
 def causal_flops(batch, heads, s, d):

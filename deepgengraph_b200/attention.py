@@ -3,6 +3,8 @@
   attn_fwd(q, k, v, causal=True, window=-1, softcap=0.0, scale=None) -> out
   attn_score_fwd(q, k, v, want_sq=False, ...)                       -> (out, colsum[, colsum_sq])
   attn_kf_fwd(q, k, v, exp_rand, tau, ...)                          -> (out, kf_score)
+  attn_snapkv_fwd(q, k, v, kernel_size=5, ...)                      -> (out, pooled colsum)
+  attn_corm_fwd(q, k, v, ...)                                       -> (out, bool flags)
 
 q [B, Sq, H, D], k/v [B, Skv, Hk, D] (fp16 or bf16, contiguous); outputs are freshly allocated
 on every call like the kernels the reference generates (to_triton.cpp:579-590): out [B, Sq, H, D]
@@ -80,6 +82,38 @@ def _attn_score_impl(q, k, v, want_sq, causal, window, softcap, scale):
   return (out, score, score_sq) if want_sq else (out, score)
 
 
+def _attn_snapkv_impl(q, k, v, kernel_size, causal, scale):
+  out, score = _attn_score_impl(q, k, v, False, causal, -1, 0.0, scale)
+  pooled = torch.empty_like(score)
+  dev = q.device
+  with torch.cuda.device(dev):
+    st = _lib.load().b200_avg_pool1d_f32(score.data_ptr(), pooled.data_ptr(), score.size(0) * score.size(1),
+                                         score.size(2), int(kernel_size), _stream_ptr(dev))
+  _lib.check(st, "attn_snapkv_fwd")
+  return out, pooled
+
+
+def _attn_corm_impl(q, k, v, causal, scale):
+  where = "attn_corm_fwd"
+  dev = _check_qkv(where, q, k, v)
+  B, Sq, H, D = q.shape
+  Skv, Hk = k.size(1), k.size(2)
+  if H != Hk:
+    raise ValueError(f"{where}: needs heads == kv heads (the reference asserts group_size == 1)")
+  if scale is None or scale <= 0:
+    scale = 1.0 / math.sqrt(D)
+  out = torch.empty_like(q)
+  score = torch.empty((B, H, Skv), dtype=torch.float32, device=dev)
+  flags = torch.empty((B, H, Skv), dtype=torch.uint8, device=dev)
+  ws, nbytes = _workspace(dev, B, Sq, Skv, H)
+  with torch.cuda.device(dev):
+    st = _lib.load().b200_attn_corm(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), score.data_ptr(),
+                                    flags.data_ptr(), ws.data_ptr(), nbytes, B, Sq, Skv, H, D, _dtype_code(q, where),
+                                    int(bool(causal)), float(scale), _stream_ptr(dev))
+  _lib.check(st, where)
+  return out, flags.view(torch.bool)
+
+
 def _attn_kf_impl(q, k, v, exp_rand, tau, causal, scale):
   where = "attn_kf_fwd"
   dev = _check_qkv(where, q, k, v)
@@ -152,6 +186,28 @@ def _(q, k, v, exp_rand, tau, causal, scale):
   return torch.empty_like(q), q.new_empty((q.size(0), k.size(2), k.size(1)), dtype=torch.float32)
 
 
+@torch.library.custom_op("b200attn::attn_snapkv_fwd", mutates_args=())
+def _op_attn_snapkv_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel_size: int, causal: bool,
+                        scale: float) -> tuple[torch.Tensor, torch.Tensor]:
+  return _attn_snapkv_impl(q, k, v, kernel_size, causal, scale)
+
+
+@_op_attn_snapkv_fwd.register_fake
+def _(q, k, v, kernel_size, causal, scale):
+  return torch.empty_like(q), q.new_empty((q.size(0), k.size(2), k.size(1)), dtype=torch.float32)
+
+
+@torch.library.custom_op("b200attn::attn_corm_fwd", mutates_args=())
+def _op_attn_corm_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool,
+                      scale: float) -> tuple[torch.Tensor, torch.Tensor]:
+  return _attn_corm_impl(q, k, v, causal, scale)
+
+
+@_op_attn_corm_fwd.register_fake
+def _(q, k, v, causal, scale):
+  return torch.empty_like(q), q.new_empty((q.size(0), k.size(2), k.size(1)), dtype=torch.bool)
+
+
 # ----------------------------------------------------------------------------------------------
 # public functions
 # ----------------------------------------------------------------------------------------------
@@ -176,3 +232,15 @@ def attn_kf_fwd(q, k, v, exp_rand, tau=1.5, causal=True, scale=None):
   """Attention output + KeyFormer score: column sums of softmax((logits - log(exp_rand)) / tau)
   (kernels/kf.py:36-42)."""
   return _op_attn_kf_fwd(q, k, v, exp_rand, float(tau), bool(causal), float(scale or 0.0))
+
+
+def attn_snapkv_fwd(q, k, v, kernel_size=5, causal=True, scale=None):
+  """Attention output + column sums average-pooled over a window of `kernel_size` keys, zero padded
+  (kernels/snapkv.py:36-38)."""
+  return _op_attn_snapkv_fwd(q, k, v, int(kernel_size), bool(causal), float(scale or 0.0))
+
+
+def attn_corm_fwd(q, k, v, causal=True, scale=None):
+  """Attention output + bool [B, H, Skv]: does any query i attend to the key with probability >= 1 / (i + 1)
+  (kernels/corm.py:35-37; the thresholds of Corm.prepare, kernels/corm.py:47-49, are evaluated in the kernel)."""
+  return _op_attn_corm_fwd(q, k, v, bool(causal), float(scale or 0.0))

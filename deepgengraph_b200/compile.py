@@ -16,6 +16,7 @@ SYSTEM = 'b200'
 _OUTPUTS = {
     'Attn': ['out'], 'Gemma2': ['out'], 'H2O': ['out', 'h2o_score'],
     'RoCo': ['out', 'roco_score', 'roco_sq_score'], 'KeyFormer': ['out', 'kf_score'],
+    'SnapKV': ['out', 'snapkv_score'], 'Corm': ['out', 'corm_score'],
 }
 
 
@@ -27,7 +28,7 @@ def compile(model, input_names, inputs, output_names, system=SYSTEM):
     raise NotImplementedError(f"no fused sm_100a kernel for core module {name}")
   if list(output_names) != _OUTPUTS[name]:
     raise ValueError(f"{name}: expected outputs {_OUTPUTS[name]}, got {list(output_names)}")
-  expect_inputs = ['q', 'k', 'v'] + (['exp_rand'] if name == 'KeyFormer' else [])
+  expect_inputs = ['q', 'k', 'v'] + {'KeyFormer': ['exp_rand'], 'Corm': ['corm_mask']}.get(name, [])
   if list(input_names) != expect_inputs:
     raise ValueError(f"{name}: expected inputs {expect_inputs}, got {list(input_names)}")
   window = getattr(model, 'window', -1)
@@ -46,6 +47,14 @@ def compile(model, input_names, inputs, output_names, system=SYSTEM):
   elif name == 'RoCo':
     def f(q, k, v):
       return _att.attn_score_fwd(q, k, v, want_sq=True, causal=True)
+  elif name == 'SnapKV':
+    ks = int(model.kernel_size)
+
+    def f(q, k, v):
+      return _att.attn_snapkv_fwd(q, k, v, kernel_size=ks, causal=True)
+  elif name == 'Corm':
+    def f(q, k, v, corm_mask=None):
+      return _att.attn_corm_fwd(q, k, v, causal=True)
   else:
     tau = float(model.tau)
 

@@ -29,6 +29,8 @@
 namespace b200 {
 
 enum SweepMode : int { SWEEP_COLSUM = 0, SWEEP_KF_COLSUM = 1, SWEEP_KF_ROWLSE = 2 };
+// second per-key statistic of the column-sum sweep: none, sum of p^2 (RoCo), or the Corm flag
+enum SweepAux : int { AUX_NONE = 0, AUX_SQUARES = 1, AUX_CORM = 2 };
 
 struct SweepParams {
   const float* lse;     // [B*H][lse_stride]  row normalisers (COLSUM: L, KF_COLSUM: Lz)
@@ -194,7 +196,7 @@ __device__ __forceinline__ void sweep_mma(const SweepCtx<Cfg>& c) {
 }
 
 // ------------------------- compute: per-key column sums -----------------------
-template <class Cfg, bool SOFTCAP, bool SQ>
+template <class Cfg, bool SOFTCAP, int AUX>
 __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, const SweepParams& p, int chunk) {
   constexpr int ST = Cfg::STAGES, BX = Cfg::BX;
   constexpr bool KF = Cfg::MODE == SWEEP_KF_COLSUM;
@@ -213,7 +215,7 @@ __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, con
   float2 acc2 = make_float2(0.f, 0.f), sq2 = make_float2(0.f, 0.f);
   // One 32-column chunk of the tile: p = exp2(x - L_i) for the thread's key against 32 queries.
   auto chunk_body = [&](auto mask_tag, const uint32_t (&sr)[32], int ch, const float* lse_s, const float* noise_col,
-                        int lo_c, int hi_c) {
+                        int lo_c, int hi_c, float qbase) {
     constexpr bool MASK = decltype(mask_tag)::value;
     const float2 c2 = make_float2(cmul, cmul);
 #pragma unroll
@@ -247,7 +249,14 @@ __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, con
       }
       const float2 p0 = make_float2(pr[0], pr[1]), p1 = make_float2(pr[2], pr[3]);
       acc2 = fadd2(acc2, fadd2(p0, p1));
-      if constexpr (SQ) sq2 = ffma2(p1, p1, ffma2(p0, p0, sq2));
+      if constexpr (AUX == AUX_SQUARES) sq2 = ffma2(p1, p1, ffma2(p0, p0, sq2));
+      if constexpr (AUX == AUX_CORM) {
+        // Corm: does any query see this key with probability >= 1 / (i + 1)?  (kernels/corm.py:35-37,47-49;
+        // tested as p * (i + 1) >= 1, the flag kept as 0/1 in the second accumulator)
+        const float q1 = qbase + (float)(ch * 32 + i);
+        sq2.x = fmaxf(sq2.x, fmaxf(pr[0] * q1 >= 1.0f ? 1.0f : 0.0f, pr[2] * (q1 + 2.0f) >= 1.0f ? 1.0f : 0.0f));
+        sq2.y = fmaxf(sq2.y, fmaxf(pr[1] * (q1 + 1.0f) >= 1.0f ? 1.0f : 0.0f, pr[3] * (q1 + 3.0f) >= 1.0f ? 1.0f : 0.0f));
+      }
     }
   };
 
@@ -273,9 +282,9 @@ __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, con
       tmem_ld_wait();
       if (ch + 1 < BX / 32) tmem_ld32(lane_addr + tb * BX + (ch + 1) * 32, sr[(ch + 1) & 1]);
       if (need_mask)
-        chunk_body(std::true_type{}, sr[ch & 1], ch, lse_s, noise_col, lo_c, hi_c);
+        chunk_body(std::true_type{}, sr[ch & 1], ch, lse_s, noise_col, lo_c, hi_c, (float)(i0 + 1));
       else
-        chunk_body(std::false_type{}, sr[ch & 1], ch, lse_s, noise_col, lo_c, hi_c);
+        chunk_body(std::false_type{}, sr[ch & 1], ch, lse_s, noise_col, lo_c, hi_c, (float)(i0 + 1));
     }
     // this TMEM buffer and this auxiliary stage may be refilled
     tc_fence_before();
@@ -288,7 +297,8 @@ __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, con
   const float acc0 = acc2.x, acc1 = acc2.y, sq0 = sq2.x, sq1 = sq2.y;
   const int64_t off = ((int64_t)c.bh * p.n_chunks + chunk) * p.kv_pad + key;
   p.partial[off] = acc0 + acc1;
-  if constexpr (SQ) p.partial_sq[off] = sq0 + sq1;
+  if constexpr (AUX == AUX_SQUARES) p.partial_sq[off] = sq0 + sq1;
+  if constexpr (AUX == AUX_CORM) p.partial_sq[off] = fmaxf(sq0, sq1);
 }
 
 // --------------------- compute: per-query log-sum-exp of z --------------------
@@ -353,7 +363,7 @@ __device__ __forceinline__ void sweep_compute_rowlse(const SweepCtx<Cfg>& c, con
 }
 
 // ----------------------------------- kernel ----------------------------------
-template <int MODE, int BX, int STAGES, bool BF16, bool SOFTCAP, bool SQ>
+template <int MODE, int BX, int STAGES, bool BF16, bool SOFTCAP, int AUX>
 __global__ void __launch_bounds__(192, 1)
 attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_x,
                   const __grid_constant__ CUtensorMap tm_n, const SweepParams p) {
@@ -399,7 +409,7 @@ attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       if (threadIdx.x < 128) {
         const int64_t off = ((int64_t)c.bh * p.n_chunks + chunk) * p.kv_pad + c.a0 + threadIdx.x;
         p.partial[off] = 0.f;
-        if constexpr (SQ) p.partial_sq[off] = 0.f;
+        if constexpr (AUX != AUX_NONE) p.partial_sq[off] = 0.f;
       }
     }
     return;
@@ -433,7 +443,7 @@ attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     if constexpr (MODE == SWEEP_KF_ROWLSE)
       sweep_compute_rowlse<Cfg>(c, p);
     else
-      sweep_compute_colsum<Cfg, SOFTCAP, SQ>(c, p, chunk);
+      sweep_compute_colsum<Cfg, SOFTCAP, AUX>(c, p, chunk);
   } else if (warp == 4) {
     if (lane == 0) sweep_producer<Cfg>(c, p, &tm_a, &tm_x, &tm_n);
   } else {
@@ -501,11 +511,11 @@ inline int64_t score_workspace_bytes(int batch, int q_len, int kv_len, int heads
   return score_workspace_layout(batch, q_len, kv_len, heads).total;
 }
 
-template <int MODE, int BX, int STAGES, bool BF16, bool SOFTCAP, bool SQ>
+template <int MODE, int BX, int STAGES, bool BF16, bool SOFTCAP, int AUX>
 int launch_sweep(const CUtensorMap& ta, const CUtensorMap& tx, const CUtensorMap& tn, const SweepParams& p,
                  int grid_x, int grid_y, cudaStream_t stream) {
   using Cfg = SweepCfg<MODE, BX, STAGES>;
-  auto kern = attn_sweep_kernel<MODE, BX, STAGES, BF16, SOFTCAP, SQ>;
+  auto kern = attn_sweep_kernel<MODE, BX, STAGES, BF16, SOFTCAP, AUX>;
   static thread_local int configured_dev = -1;
   int dev = 0;
   B200_CUDA_TRY(cudaGetDevice(&dev));
@@ -533,10 +543,41 @@ inline int score_common_checks(const void* q, const void* k, const void* v, void
   return B200_OK;
 }
 
+// Flags of the Corm variant: out[bh][j] = (max over chunks of the 0/1 partial flags) != 0.
+__global__ void __launch_bounds__(256)
+corm_reduce_kernel(uint8_t* __restrict__ out, const float* __restrict__ partial_flag, int kv_len, int kv_pad,
+                   int n_chunks) {
+  const int bh = blockIdx.y;
+  const int j = blockIdx.x * 256 + threadIdx.x;
+  if (j >= kv_len) return;
+  const float* src = partial_flag + (int64_t)bh * n_chunks * kv_pad + j;
+  float a = 0.f;
+  for (int cidx = 0; cidx < n_chunks; ++cidx) a = fmaxf(a, src[(int64_t)cidx * kv_pad]);
+  out[(int64_t)bh * kv_len + j] = a != 0.f ? 1 : 0;
+}
+
+// out[r][j] = (1 / kernel) * sum_{d = -kernel/2 .. kernel/2} in[r][j + d], zero padded (SnapKV's pooling of
+// the column sums: F.avg_pool1d(kernel_size, padding = kernel_size // 2, stride = 1), kernels/snapkv.py:36-38)
+__global__ void __launch_bounds__(256)
+avg_pool1d_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t rows, int len, int kernel) {
+  const int64_t r = blockIdx.y;
+  const int j = blockIdx.x * 256 + threadIdx.x;
+  if (j >= len) return;
+  const float* row = in + r * len;
+  const int half = kernel / 2;
+  float a = 0.f;
+  for (int d = -half; d <= half; ++d) {
+    const int jj = j + d;
+    if (jj >= 0 && jj < len) a += row[jj];
+  }
+  out[r * len + j] = a / (float)kernel;
+}
+
+// corm_flags (optional): uint8 [B, H, Skv]; when given, the second statistic is the Corm flag and score_sq must be null.
 inline int attn_score_impl(const void* q, const void* k, const void* v, void* out, float* score, float* score_sq,
                            void* workspace, int64_t workspace_bytes, int batch, int q_len, int kv_len, int heads,
                            int head_dim, int dtype, int causal, int window, float softcap, float scale,
-                           cudaStream_t stream) {
+                           cudaStream_t stream, uint8_t* corm_flags = nullptr) {
   int rc = score_common_checks(q, k, v, out, workspace, workspace_bytes, batch, q_len, kv_len, heads, head_dim, dtype);
   if (rc != B200_OK) return rc;
   if (!score) return B200_ERR_BAD_ARGUMENT;
@@ -576,16 +617,19 @@ inline int attn_score_impl(const void* q, const void* k, const void* v, void* ou
   p.cap_in = softcap > 0.f ? scale / softcap : 0.f;
   p.cap_out = softcap * kLog2e;
   p.inv_tau = 1.0f;
+  if (corm_flags != nullptr && (score_sq != nullptr || softcap > 0.f)) return B200_ERR_BAD_ARGUMENT;
   const bool cap = softcap > 0.f, sq = score_sq != nullptr;
   const int gy = w.kv_pad / 128;
 
-#define B200_SWEEP0(BF, CAP, SQF) launch_sweep<SWEEP_COLSUM, 128, 2, BF, CAP, SQF>(ta, tx, tn, p, p.n_chunks, gy, stream)
-  if (bf16)
-    rc = cap ? (sq ? B200_SWEEP0(true, true, true) : B200_SWEEP0(true, true, false))
-             : (sq ? B200_SWEEP0(true, false, true) : B200_SWEEP0(true, false, false));
+#define B200_SWEEP0(BF, CAP, AUXV) launch_sweep<SWEEP_COLSUM, 128, 2, BF, CAP, AUXV>(ta, tx, tn, p, p.n_chunks, gy, stream)
+  if (corm_flags != nullptr)
+    rc = bf16 ? B200_SWEEP0(true, false, AUX_CORM) : B200_SWEEP0(false, false, AUX_CORM);
+  else if (bf16)
+    rc = cap ? (sq ? B200_SWEEP0(true, true, AUX_SQUARES) : B200_SWEEP0(true, true, AUX_NONE))
+             : (sq ? B200_SWEEP0(true, false, AUX_SQUARES) : B200_SWEEP0(true, false, AUX_NONE));
   else
-    rc = cap ? (sq ? B200_SWEEP0(false, true, true) : B200_SWEEP0(false, true, false))
-             : (sq ? B200_SWEEP0(false, false, true) : B200_SWEEP0(false, false, false));
+    rc = cap ? (sq ? B200_SWEEP0(false, true, AUX_SQUARES) : B200_SWEEP0(false, true, AUX_NONE))
+             : (sq ? B200_SWEEP0(false, false, AUX_SQUARES) : B200_SWEEP0(false, false, AUX_NONE));
 #undef B200_SWEEP0
   if (rc != B200_OK) return rc;
 
@@ -593,6 +637,10 @@ inline int attn_score_impl(const void* q, const void* k, const void* v, void* ou
   score_reduce_kernel<<<rgrid, 256, 0, stream>>>(score, score_sq, p.partial, p.partial_sq, kv_len, w.kv_pad,
                                                  p.n_chunks);
   B200_CUDA_TRY(cudaGetLastError());
+  if (corm_flags != nullptr) {
+    corm_reduce_kernel<<<rgrid, 256, 0, stream>>>(corm_flags, p.partial_sq, kv_len, w.kv_pad, p.n_chunks);
+    B200_CUDA_TRY(cudaGetLastError());
+  }
   return B200_OK;
 }
 

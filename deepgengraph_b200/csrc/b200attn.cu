@@ -224,6 +224,25 @@ int b200_attn_score(const void* q, const void* k, const void* v, void* out, floa
                          head_dim, dtype, causal, window, softcap, scale, (cudaStream_t)stream);
 }
 
+int b200_attn_corm(const void* q, const void* k, const void* v, void* out, float* score, uint8_t* corm_flags,
+                   void* workspace, int64_t workspace_bytes, int batch, int q_len, int kv_len, int heads,
+                   int head_dim, int dtype, int causal, float scale, void* stream) {
+  if (!corm_flags) return B200_ERR_BAD_ARGUMENT;
+  return attn_score_impl(q, k, v, out, score, nullptr, workspace, workspace_bytes, batch, q_len, kv_len, heads,
+                         head_dim, dtype, causal, 0, 0.f, scale, (cudaStream_t)stream, corm_flags);
+}
+
+int b200_avg_pool1d_f32(const float* input, float* output, int64_t rows, int length, int kernel_size, void* stream) {
+  if (!input || !output || rows < 0 || length <= 0 || kernel_size <= 0 || (kernel_size & 1) == 0)
+    return B200_ERR_BAD_ARGUMENT;
+  if (rows == 0) return B200_OK;
+  if (rows > 65535) return B200_ERR_UNSUPPORTED;
+  dim3 grid((length + 255) / 256, (unsigned)rows);
+  avg_pool1d_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(input, output, rows, length, kernel_size);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
 int b200_attn_kf_score(const void* q, const void* k, const void* v, const float* exp_rand, void* out,
                        float* kf_score, void* workspace, int64_t workspace_bytes, int batch, int q_len, int kv_len,
                        int heads, int head_dim, int dtype, int causal, float tau, float scale, void* stream) {

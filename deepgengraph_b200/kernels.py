@@ -124,10 +124,47 @@ class KeyFormer(_CoreModule):
     return {'input': OrderedDict(q=q, k=k, v=v, exp_rand=exp_rand), 'output': ['out', 'kf_score']}
 
 
+class SnapKV(_CoreModule):
+  """Attention + column sums smoothed by a 1-D average pool over the keys (kernels/snapkv.py:18-38)."""
+
+  def __init__(self, kernel_size=5, kv_head_num=32, head_num=32, head_dim=128):
+    super().__init__(kv_head_num, head_num, head_dim)
+    self.kernel_size = kernel_size
+    assert self.group_size == 1
+
+  def forward(self, q, k, v):
+    return _att.attn_snapkv_fwd(q, k, v, kernel_size=self.kernel_size, causal=True)
+
+  def prepare(self, batch_size=1, q_len=4096, kv_len=4096, dtype=torch.float16, device=None):
+    q, k, v, _ = self._qkv(batch_size, q_len, kv_len, dtype, device, torch.randn)
+    return {'input': OrderedDict(q=q, k=k, v=v), 'output': ['out', 'snapkv_score']}
+
+
+class Corm(_CoreModule):
+  """Attention + per-key flag: some query i attends to the key with probability >= 1 / (i + 1)
+  (kernels/corm.py:18-37).  `corm_mask` keeps the reference's signature: it must be the tensor Corm.prepare
+  builds (row i filled with 1 / (i + 1), kernels/corm.py:47-49); the kernel evaluates those thresholds itself."""
+
+  def __init__(self, kv_head_num=32, head_num=32, head_dim=128):
+    super().__init__(kv_head_num, head_num, head_dim)
+    assert self.group_size == 1
+
+  def forward(self, q, k, v, corm_mask=None):
+    return _att.attn_corm_fwd(q, k, v, causal=True)
+
+  def prepare(self, batch_size=1, q_len=4096, kv_len=4096, dtype=torch.float16, device=None):
+    q, k, v, device = self._qkv(batch_size, q_len, kv_len, dtype, device, torch.randn)
+    rows = 1.0 / torch.arange(1, q_len + 1, dtype=torch.float32, device=device)
+    corm_mask = rows[:, None].expand(q_len, kv_len).contiguous()
+    return {'input': OrderedDict(q=q, k=k, v=v, corm_mask=corm_mask), 'output': ['out', 'corm_score']}
+
+
 KERNEL_ZOO = {
     'attn': Attn,
+    'corm': Corm,
     'gemma2': Gemma2,
     'h2o': H2O,
     'kf': KeyFormer,
     'roco': RoCo,
+    'snapkv': SnapKV,
 }

@@ -149,6 +149,25 @@ int b200_attn_score_static(const void* q, const void* k, const void* v, void* ou
                            int dtype, int causal, int window, float softcap, float scale, void* stream);
 
 /*
+ * Corm: attention output, the column sums `score` (workspace by-product, required) and
+ *   corm_flags[b, h, j] = any_i( p_ij >= 1 / (i + 1) )     -- Corm.forward kernels/corm.py:35-37
+ * uint8 [batch, heads, kv_len] (1 = true).  The reference passes the thresholds as a [q_len, kv_len] tensor
+ * built by Corm.prepare (kernels/corm.py:47-49: row i holds 1 / (i + 1)); this entry point evaluates the same
+ * thresholds in the kernel (tested as p * (i + 1) >= 1).
+ */
+int b200_attn_corm(const void* q, const void* k, const void* v, void* out, float* score,
+                   uint8_t* corm_flags, void* workspace, int64_t workspace_bytes, int batch, int q_len,
+                   int kv_len, int heads, int head_dim, int dtype, int causal, float scale, void* stream);
+
+/*
+ * out[r, j] = mean over the window of `kernel_size` (odd) centred on j of in[r, :], zero padded, divisor
+ * kernel_size -- the pooling SnapKV applies to the column sums (kernels/snapkv.py:36-38:
+ * F.avg_pool1d(kernel_size=5, padding=2, stride=1)).  float32 [rows, length].
+ */
+int b200_avg_pool1d_f32(const float* input, float* output, int64_t rows, int length, int kernel_size,
+                        void* stream);
+
+/*
  * KeyFormer: attention output plus
  *   kf_score[b, h, j] = sum_i softmax_j((logit_ij - log(exp_rand_ij)) / tau)
  *   -- KeyFormer.forward kernels/kf.py:19-42

@@ -84,6 +84,35 @@ def test_keyformer_scores_match_oracle(cuda_device, shape, tau):
   torch.testing.assert_close(s.sum(-1).cpu(), torch.full((B, H), float(Sq)), rtol=1e-4, atol=1e-3)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_snapkv_and_corm_golden_cases_of_the_reference_modules(cuda_device, dtype):
+  inp = {k: t.to(cuda_device) for k, t in cases.make_inputs("snapkv_s192", dtype).items()}
+  g = np.load(os.path.join(HERE, "golden", "snapkv_s192.npz"))
+  out, pooled = att.attn_snapkv_fwd(inp["q"], inp["k"], inp["v"], kernel_size=5)
+  torch.testing.assert_close(out.float().cpu()[:, ::cases.ROW_STRIDE], torch.from_numpy(g["out_rows"]), **TOL)
+  torch.testing.assert_close(pooled.cpu(), torch.from_numpy(g["score0"]), **STOL)
+  inp = {k: t.to(cuda_device) for k, t in cases.make_inputs("corm_s192", dtype).items()}
+  g = np.load(os.path.join(HERE, "golden", "corm_s192.npz"))
+  out, flags = att.attn_corm_fwd(inp["q"], inp["k"], inp["v"])
+  assert flags.dtype == torch.bool and tuple(flags.shape) == (1, 2, 192)
+  torch.testing.assert_close(out.float().cpu()[:, ::cases.ROW_STRIDE], torch.from_numpy(g["out_rows"]), **TOL)
+  # exact thresholds: allow a flip only where a probability sits within rounding of 1 / (i + 1)
+  assert (flags.cpu().numpy() != g["score0"]).mean() <= 0.01
+
+
+@pytest.mark.parametrize("shape", [(1, 640, 640, 2), (2, 300, 300, 3), (1, 1500, 1500, 2)])
+def test_snapkv_and_corm_match_oracle(cuda_device, shape):
+  B, Sq, Skv, H = shape
+  q, k, v = _qkv(B, Sq, Skv, H, 128, torch.bfloat16, seed=sum(shape) + 5)
+  ref = rm.attention_ref(q, k, v, want=("out", "snapkv", "corm", "colsum"))
+  out, pooled = att.attn_snapkv_fwd(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device))
+  torch.testing.assert_close(pooled.cpu(), ref["snapkv"], **STOL)
+  out2, flags = att.attn_corm_fwd(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device))
+  torch.testing.assert_close(out2.float().cpu(), ref["out"], **TOL)
+  assert (flags.cpu() != ref["corm"]).float().mean().item() <= 0.01
+  assert flags.any() and not flags.all()
+
+
 def test_config3_slice_full_length(cuda_device):
   q, k, v = _qkv(1, 4096, 4096, 2, 128, torch.bfloat16, seed=12)
   ref = rm.attention_ref(q, k, v, want=("out", "colsum"), head_chunk=1)
