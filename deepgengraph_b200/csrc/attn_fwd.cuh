@@ -239,33 +239,45 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<Cfg, BF16>& c) {
     }
     __syncwarp();
   };
-  auto v_item = [&](int n) {   // O += P(j) V(j)
-    const int j = c.jmin + n, slot = item % SL, ph = (item / SL) & 1;
+  // Steady state, one step per key block n: [O += P(n) V(n)] and [S(n+SB) = Q K(n+SB)^T] are issued back to
+  // back by one elected lane.  The ring slots of both operands were filled long before, so their FULL barriers
+  // are observed FIRST; the wait for P(n) -- the only barrier that completes late -- comes last, and nothing
+  // but a fence stands between its completion and the twelve MMAs.  (tcgen05 issue is synchronous with the
+  // tensor pipe once its queue is full, so every barrier round trip between the two GEMMs used to add to the
+  // P(n) -> S(n+SB) latency that the softmax of block n+1 has to cover.)
+  auto step = [&](int n, int nb) {
+    const int jv = c.jmin + n, vslot = item % SL, vph = (item / SL) & 1;
     ++item;
-    const bool act = j >= lo && j < hi;
-    const int nt = j - lo, buf = nt % SB;
+    const bool has_k = n + SB < nb;
+    const int jk = c.jmin + n + SB, kslot = item % SL, kph = (item / SL) & 1;
+    if (has_k) ++item;
+    const bool act_v = jv >= lo && jv < hi;
+    const bool act_k = has_k && jk >= lo && jk < hi;
+    const int nt = jv - lo, buf = nt % SB;
     if (elect_one()) B200_TL((3 * 64 + (n & 63)) * 8 + T * 4 + 0);
-    if (act) ok = mbar_wait(&c.bars[Cfg::BAR_P_FULL + T * SB + buf], (nt / SB) & 1, c.abort_flag, WAIT_P_FULL);
-    if (elect_one()) B200_TL((3 * 64 + (n & 63)) * 8 + T * 4 + 1);
-    ok = ok && mbar_wait(&c.bars[Cfg::BAR_FULL + slot], ph, c.abort_flag, WAIT_V_FULL);
+    ok = mbar_wait(&c.bars[Cfg::BAR_FULL + vslot], vph, c.abort_flag, WAIT_V_FULL);
+    if (ok && has_k) ok = mbar_wait(&c.bars[Cfg::BAR_FULL + kslot], kph, c.abort_flag, WAIT_K_FULL);
+    if (ok && act_k && !q_ready) {
+      ok = mbar_wait(&c.bars[Cfg::BAR_Q_FULL + T], 0, c.abort_flag, WAIT_Q_FULL);
+      q_ready = true;
+    }
+    if (ok && act_v) ok = mbar_wait(&c.bars[Cfg::BAR_P_FULL + T * SB + buf], (nt / SB) & 1, c.abort_flag, WAIT_P_FULL);
     if (!ok) return;
     tc_fence_after();
     if (elect_one()) {
-      if (act) {
-        B200_TL((2 * 64 + (n & 63)) * 8 + T * 4 + 0);
-        issue_pv(slot, buf, nt);
-        B200_TL((2 * 64 + (n & 63)) * 8 + T * 4 + 1);
-      }
-      umma_commit(&c.bars[Cfg::BAR_EMPTY + slot]);   // V(j) consumed by this tile
+      B200_TL((3 * 64 + (n & 63)) * 8 + T * 4 + 1);
+      if (act_v) issue_pv(vslot, buf, nt);
+      B200_TL((2 * 64 + (n & 63)) * 8 + T * 4 + 1);
+      if (act_k) issue_s(kslot, (jk - lo) % SB);
+      B200_TL((2 * 64 + (n & 63)) * 8 + T * 4 + 3);
+      umma_commit(&c.bars[Cfg::BAR_EMPTY + vslot]);              // V(n) consumed by this tile
+      if (has_k) umma_commit(&c.bars[Cfg::BAR_EMPTY + kslot]);   // K(n+SB) consumed by this tile
     }
     __syncwarp();
   };
   const int nb = c.jmax - c.jmin;
   for (int n = 0; n < SB && n < nb && ok; ++n) k_item(n);
-  for (int n = 0; n < nb && ok; ++n) {
-    v_item(n);
-    if (ok && n + SB < nb) k_item(n + SB);
-  }
+  for (int n = 0; n < nb && ok; ++n) step(n, nb);
   // every MMA issued above has retired before the CTA tears TMEM down
   if (elect_one()) umma_commit(&c.bars[Cfg::BAR_DRAIN + T]);
   __syncwarp();
@@ -495,9 +507,11 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<Cfg, BF16>& c, const Fw
   }
 
   // epilogue: O / l -> 16-bit -> global (BSHD), base-2 LSE for the score passes
+  if ((threadIdx.x & 127) == 0) B200_TL((3 * 64 + 62) * 8 + 2);   // last block's P delivered
   const int last = rng.hi - rng.lo - 1;
   if (!mbar_wait(o_full + (last & 1), (last >> 1) & 1, c.abort_flag, WAIT_O_FULL)) return;
   tc_fence_after();
+  if ((threadIdx.x & 127) == 0) B200_TL((3 * 64 + 62) * 8 + 3);   // last P V complete
   const float inv_l = 1.0f / l;
   const bool in_range = row < p.q_len;
   uint4* out_row = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) +
@@ -519,6 +533,7 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<Cfg, BF16>& c, const Fw
       }
     }
   }
+  if ((threadIdx.x & 127) == 0) B200_TL((3 * 64 + 62) * 8 + 4);   // output stored
   if (p.lse != nullptr && in_range) p.lse[((int64_t)c.b * p.heads + c.h) * p.lse_stride + row] = m + log2f(l);
 }
 
@@ -538,6 +553,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __syncthreads();
   if (s_skip != 0) return;
   B200_TL_INIT();
+  if (threadIdx.x == 0) B200_TL((3 * 64 + 62) * 8 + 0);   // kernel entry
 
   FwdCtx<Cfg, BF16> c;
   c.sQ = smem;
@@ -588,6 +604,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   c.tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) B200_TL((3 * 64 + 62) * 8 + 1);   // set-up done (barriers, TMEM)
 
   if (warp < NQ * 4) {
     if constexpr (Cfg::REBALANCE_REGS) reg_alloc<224>();
@@ -613,6 +630,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) B200_TL((3 * 64 + 62) * 8 + 5);   // all roles done
   if (warp == 0) tmem_dealloc(c.tmem_base, Cfg::TMEM_COLS);
   B200_TL_FLUSH();
 }
