@@ -26,6 +26,7 @@ SIGNATURES = {
     "b200_last_cuda_error": (_i, []),
     "b200_abi_version": (_i, []),
     "b200_device_status": (_i, [ctypes.POINTER(_i)]),
+    "b200_selftest_bounded_wait": (_i, [_i, _vp, _vp]),
     "b200_rms_norm": (_i, [_vp, _vp, _vp, _f, _i64, _i, _i, _vp]),
     "b200_fused_add_rms_norm": (_i, [_vp, _vp, _vp, _f, _i64, _i, _i, _vp]),
     "b200_silu_and_mul": (_i, [_vp, _vp, _i64, _i, _i, _vp]),

@@ -65,6 +65,21 @@ int make_f32_matrix_tensor_map(CUtensorMap* map, const void* base, int64_t rows,
   return B200_OK;
 }
 
+// Self-test of the bounded-wait machinery: one warp waits on an mbarrier that nobody ever arrives on.  The wait
+// gives up after `limit_ns`, records WAIT_SELFTEST in the device status word and the kernel ends normally.
+__global__ void bounded_wait_selftest_kernel(uint64_t limit_ns, int* gave_up) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const bool ok = mbar_try_wait(&bar, 0) || mbar_wait_slow(&bar, 0, &abort_flag, WAIT_SELFTEST, limit_ns);
+  if (threadIdx.x == 0 && gave_up != nullptr) *gave_up = ok ? 0 : 1;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Built-in scratch of b200_attn_score_static: a fixed array in the library's device image, so that callers
 // which must not allocate device memory still have somewhere to put the row normalisers and partial sums.
@@ -126,6 +141,13 @@ int b200_device_status(int* status_out) {
   }
   *status_out = word;
   return word == 0 ? B200_OK : B200_ERR_DEVICE_TIMEOUT;
+}
+
+int b200_selftest_bounded_wait(int limit_ms, int* gave_up_device, void* stream) {
+  if (limit_ms <= 0 || limit_ms > 1000) return B200_ERR_BAD_ARGUMENT;
+  bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((uint64_t)limit_ms * 1000000ull, gave_up_device);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
 }
 
 int b200_rms_norm(void* out, const void* input, const void* weight, float epsilon, int64_t num_tokens,

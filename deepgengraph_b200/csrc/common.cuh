@@ -83,7 +83,8 @@ enum WaitCode : int {
   WAIT_N_FULL = 13,   // noise tile
   WAIT_N_EMPTY = 14,
   WAIT_DRAIN = 15,
-  WAIT_TURN = 16      // exp-phase turn-taking between the two query tiles
+  WAIT_TURN = 16,     // exp-phase turn-taking between the two query tiles
+  WAIT_SELFTEST = 17  // b200_selftest_bounded_wait
 };
 
 // ---------------------------------------------------------------------------
@@ -147,13 +148,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 __device__ __forceinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                            int code) {
+                                            int code, uint64_t limit_ns = kWaitLimitNs) {
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0xff) == 0) {
       if (*abort_flag != 0) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      if (global_timer_ns() - t0 > limit_ns) {
         *abort_flag = code;
         atomicCAS(&g_device_status, 0, code | (int)((blockIdx.x & 0xffffff) << 8));
         return false;

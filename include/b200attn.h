@@ -55,6 +55,15 @@ int b200_abi_version(void);
  */
 int b200_device_status(int* status_out);
 
+/*
+ * Self-test of the bounded device-side waits (no counterpart in the reference, which has no failure handling:
+ * compile.py:207-212 swallows errors).  Launches one warp that waits on a barrier nobody signals; after
+ * `limit_ms` (1..1000) the wait gives up, the kernel ends normally, *gave_up_device (device int, may be NULL)
+ * becomes 1 and the device status word holds code 17, which the next b200_device_status call reports as
+ * B200_ERR_DEVICE_TIMEOUT and clears.  The GPU stays fully usable: nothing traps and nothing hangs.
+ */
+int b200_selftest_bounded_wait(int limit_ms, int* gave_up_device, void* stream);
+
 /* ------------------------------------------------------------------------- *
  * Bandwidth ops.  Replace the reference's csrc/ natives
  * (csrc/ffi.cpp:4-8, csrc/op.h:2-6).
