@@ -244,3 +244,27 @@ def attn_corm_fwd(q, k, v, causal=True, scale=None):
   """Attention output + bool [B, H, Skv]: does any query i attend to the key with probability >= 1 / (i + 1)
   (kernels/corm.py:35-37; the thresholds of Corm.prepare, kernels/corm.py:47-49, are evaluated in the kernel)."""
   return _op_attn_corm_fwd(q, k, v, bool(causal), float(scale or 0.0))
+
+
+def kv_evict_topk(score, k, v, budget, return_indices=False):
+  """KV-cache eviction step of the reference's model glue (models/h2o.py:51-57, models/kf.py:54-60): per (batch,
+  head) keep the `budget` keys with the largest score, in position order.
+  score float32 [B, H, S]; k, v [B, S, H, D].  Returns kv_cache [B, 2, budget, H, D] (plane 0 keys, plane 1
+  values) and, if asked, the selected positions int32 [B, H, budget]."""
+  where = "kv_evict_topk"
+  dev = _require_cuda(where, score, k, v)
+  if score.dtype != torch.float32 or score.dim() != 3 or not score.is_contiguous():
+    raise ValueError(f"{where}: score must be contiguous float32 [batch, heads, seq]")
+  if k.dim() != 4 or k.shape != v.shape or k.dtype != v.dtype or not (k.is_contiguous() and v.is_contiguous()):
+    raise ValueError(f"{where}: k, v must be contiguous [batch, seq, heads, head_dim] of one dtype")
+  B, S, H, D = k.shape
+  if tuple(score.shape) != (B, H, S):
+    raise ValueError(f"{where}: score shape {tuple(score.shape)} does not match k {tuple(k.shape)}")
+  kv_cache = torch.empty((B, 2, int(budget), H, D), dtype=k.dtype, device=dev)
+  idx = torch.empty((B, H, int(budget)), dtype=torch.int32, device=dev) if return_indices else None
+  with torch.cuda.device(dev):
+    st = _lib.load().b200_kv_evict_topk(score.data_ptr(), k.data_ptr(), v.data_ptr(), kv_cache.data_ptr(),
+                                        idx.data_ptr() if return_indices else None, B, S, H, D, int(budget),
+                                        _dtype_code(k, where), _stream_ptr(dev))
+  _lib.check(st, where)
+  return (kv_cache, idx) if return_indices else kv_cache

@@ -9,6 +9,7 @@
 #include "elementwise.cuh"
 #include "attn_fwd.cuh"
 #include "attn_sweep.cuh"
+#include "kv_evict.cuh"
 
 namespace b200 {
 
@@ -263,6 +264,14 @@ int b200_avg_pool1d_f32(const float* input, float* output, int64_t rows, int len
   avg_pool1d_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(input, output, rows, length, kernel_size);
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
+}
+
+int b200_kv_evict_topk(const float* score, const void* k, const void* v, void* kv_cache, int32_t* indices,
+                       int batch, int seq_len, int heads, int head_dim, int budget, int dtype, void* stream) {
+  const int elem = dtype == B200_F32 ? 4 : (dtype == B200_F16 || dtype == B200_BF16) ? 2 : 0;
+  if (elem == 0) return B200_ERR_BAD_DTYPE;
+  return kv_evict_topk_impl(score, k, v, kv_cache, indices, batch, seq_len, heads, head_dim, budget, elem,
+                            (cudaStream_t)stream);
 }
 
 int b200_attn_kf_score(const void* q, const void* k, const void* v, const float* exp_rand, void* out,

@@ -177,6 +177,19 @@ int b200_avg_pool1d_f32(const float* input, float* output, int64_t rows, int len
                         void* stream);
 
 /*
+ * KV-cache eviction after a score-producing variant: per (batch, head) keep the `budget` keys with the largest
+ * score, in ascending key order, and gather their rows
+ *   -- deepgengraph_exp/cases/models/h2o.py:51-57, models/kf.py:54-60 (topk -> sort -> gather -> cat).
+ * score    float32 [batch, heads, seq_len]
+ * k, v     [batch, seq_len, heads, head_dim]   (dtype gives the element size only)
+ * kv_cache [batch, 2, budget, heads, head_dim] (plane 0 = keys, plane 1 = values)
+ * indices  int32 [batch, heads, budget], optional (may be NULL): the selected key positions, ascending
+ * Ties at the budget-th score keep the lower key index.  budget <= min(seq_len, 12288).
+ */
+int b200_kv_evict_topk(const float* score, const void* k, const void* v, void* kv_cache, int32_t* indices,
+                       int batch, int seq_len, int heads, int head_dim, int budget, int dtype, void* stream);
+
+/*
  * KeyFormer: attention output plus
  *   kf_score[b, h, j] = sum_i softmax_j((logit_ij - log(exp_rand_ij)) / tau)
  *   -- KeyFormer.forward kernels/kf.py:19-42

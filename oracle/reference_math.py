@@ -105,6 +105,20 @@ def attention_ref(q, k, v, causal=True, window=0, softcap=0.0, scale=None, exp_r
   return res
 
 
+def kv_evict_topk_ref(score, k, v, budget):
+  """KV-cache eviction of the reference's model glue, verbatim semantics
+  (deepgengraph_exp/cases/models/h2o.py:51-57): topk(score, budget) -> sort the indices -> gather k and v rows ->
+  cat([k_cache, v_cache], dim=1).  score [B, H, S] fp32, k/v [B, S, H, D].  Returns (kv_cache [B, 2, budget, H, D],
+  sorted indices [B, H, budget])."""
+  B, S, H, D = k.shape
+  _, sel = torch.topk(score, k=budget, dim=-1, sorted=True)
+  sel = sel.sort(dim=-1)[0]                                            # [B, H, budget]
+  index = sel.transpose(1, 2)[:, :, :, None].expand(B, budget, H, D)
+  k_cache = torch.gather(k, dim=1, index=index).view(B, 1, budget, H, D)
+  v_cache = torch.gather(v, dim=1, index=index).view(B, 1, budget, H, D)
+  return torch.cat([k_cache, v_cache], dim=1), sel
+
+
 # --------------------------------------------------------------------------------------------
 # csrc/ ops.  Semantic truth = the CUDA sources (csrc/norm.cu, activation.cu, pos_encoding.cu);
 # the Python stand-ins in deepgengraph_exp/cases/models/llama_base.py discard their results.

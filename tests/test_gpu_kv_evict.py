@@ -1,0 +1,46 @@
+"""KV-cache eviction (top-`budget` keys by score, position order, gathered K/V rows) against the oracle's verbatim
+restatement of the reference's topk -> sort -> gather.  Index work: bit-exact."""
+import pytest
+import torch
+
+from deepgengraph_b200 import attention as att
+from oracle import reference_math as rm
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("shape,budget", [((1, 4096, 32, 128), 512), ((2, 1000, 3, 128), 1), ((2, 1000, 3, 128), 1000),
+                                           ((1, 777, 2, 64), 300), ((1, 2048, 4, 256), 512)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_matches_topk_sort_gather(cuda_device, shape, budget, dtype):
+  B, S, H, D = shape
+  g = torch.Generator().manual_seed(S + budget)
+  score = torch.rand(B, H, S, generator=g) * 10 - 2          # distinct values with overwhelming probability
+  k = torch.randn(B, S, H, D, generator=g).to(dtype)
+  v = torch.randn(B, S, H, D, generator=g).to(dtype)
+  ref_cache, ref_idx = rm.kv_evict_topk_ref(score, k, v, budget)
+  cache, idx = att.kv_evict_topk(score.to(cuda_device), k.to(cuda_device), v.to(cuda_device), budget,
+                                 return_indices=True)
+  assert torch.equal(idx.cpu().long(), ref_idx)
+  assert torch.equal(cache.cpu(), ref_cache)
+
+
+def test_scores_from_the_fused_kernel_and_ties(cuda_device):
+  # end to end: H2O scores from the fused kernel feed the eviction, as in the reference's model glue
+  g = torch.Generator().manual_seed(3)
+  q, k, v = (torch.randn(1, 1024, 2, 128, generator=g).to(torch.bfloat16).to(cuda_device) for _ in range(3))
+  _, score = att.attn_score_fwd(q, k, v)
+  cache, idx = att.kv_evict_topk(score, k, v, 256, return_indices=True)
+  ref_cache, ref_idx = rm.kv_evict_topk_ref(score.cpu(), k.cpu(), v.cpu(), 256)
+  assert torch.equal(idx.cpu().long(), ref_idx) and torch.equal(cache.cpu(), ref_cache)
+  # ties: all scores equal -> any `budget` keys are a valid top-k; this kernel keeps the lowest positions
+  flat = torch.ones(1, 2, 500, device=cuda_device)
+  kk = torch.randn(1, 500, 2, 128, device=cuda_device, dtype=torch.bfloat16)
+  cache, idx = att.kv_evict_topk(flat, kk, kk, 100, return_indices=True)
+  assert torch.equal(idx.cpu(), torch.arange(100, dtype=torch.int32).expand(1, 2, 100))
+  assert torch.equal(cache[:, 0], kk[:, :100])
+  # negative values and zeros order correctly
+  sc = torch.tensor([[[-3.0, 0.0, -0.0, 5.0, -1.0, 2.0, -7.0, 1.0]]], device=cuda_device)
+  kk = torch.randn(1, 8, 1, 128, device=cuda_device, dtype=torch.bfloat16)
+  _, idx = att.kv_evict_topk(sc, kk, kk, 3, return_indices=True)
+  assert idx.cpu().tolist() == [[[3, 5, 7]]]
