@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(CSRC, "libb200attn.so")
 SOURCES = ["b200attn.cu"]
-DEPS = ["b200attn.cu", "common.cuh", "elementwise.cuh", "attn_fwd.cuh", "attn_sweep.cuh", "kv_evict.cuh",
+DEPS = ["b200attn.cu", "common.cuh", "elementwise.cuh", "attn_fwd.cuh", "attn_fwd_persist.cuh", "attn_sweep.cuh", "kv_evict.cuh",
         os.path.join("..", "..", "include", "b200attn.h")]
 
 

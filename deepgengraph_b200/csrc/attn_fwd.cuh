@@ -329,8 +329,10 @@ constexpr bool kTakeTurns = B200_TAKE_TURNS != 0;
 template <class Cfg, bool BF16, bool SOFTCAP, bool MASK>
 __device__ __forceinline__ bool fwd_softmax_block(const FwdCtx<Cfg, BF16>& c, const FwdParams& p, uint32_t s_addr,
                                                   uint32_t o_addr, uint64_t* o_full, uint64_t* p_full, int n,
-                                                  int lo_c, int hi_c, float cmul, float& m, float& l,
-                                                  uint64_t* turn_wait, int turn_parity, uint64_t* turn_pass) {
+                                                  int g, int lo_c, int hi_c, float cmul, float& m, float& l,
+                                                  uint64_t* turn_wait, int turn_parity, uint64_t* turn_pass,
+                                                  uint64_t* next_s_full = nullptr, int next_parity = 0,
+                                                  bool* next_ready = nullptr) {
   constexpr int D = Cfg::D, BN = Cfg::BN;
   const int lane = threadIdx.x & 31;
   [[maybe_unused]] const int tl_base = (((int)(threadIdx.x >> 7)) * 64 + (n & 63)) * 8;
@@ -381,7 +383,8 @@ __device__ __forceinline__ bool fwd_softmax_block(const FwdCtx<Cfg, BF16>& c, co
     // P V(n-1): barrier (n-1) % 2, phase (n-1) / 2.  S(n) has completed, hence every earlier MMA of this tile up to
     // P V(n-2) too, and P V(n+1) cannot start before this thread delivers P(n): the barrier is exactly in or
     // just past the awaited phase.
-    if (!mbar_wait(o_full + ((n - 1) & 1), ((n - 1) >> 1) & 1, c.abort_flag, WAIT_O_FULL)) return false;
+    // (g counts the P V products of this CTA: equal to n unless the CTA walks several tiles)
+    if (!mbar_wait(o_full + ((g - 1) & 1), ((g - 1) >> 1) & 1, c.abort_flag, WAIT_O_FULL)) return false;
     tc_fence_after();
     const float2 a2 = make_float2(alpha, alpha);
 #pragma unroll
@@ -402,6 +405,9 @@ __device__ __forceinline__ bool fwd_softmax_block(const FwdCtx<Cfg, BF16>& c, co
   // sub-partition shares: the two take turns (see fwd_softmax), so that one tile's exponentials overlap the
   // other tile's MMAs instead of colliding with its exponentials.
   if (turn_wait != nullptr && !mbar_wait(turn_wait, turn_parity, c.abort_flag, WAIT_TURN)) return false;
+  // Early look at the next block's S barrier: shared-memory latency is ~10x higher while the S = Q K^T MMAs
+  // saturate the shared-memory port, so the probe is issued here and its result consumed after the exponentials.
+  if (next_s_full != nullptr) *next_ready = mbar_test_wait(next_s_full, next_parity);
   // P = exp2(x - m), packed to the 16-bit input type, written over the first BN/2 columns of S
   const float2 c2 = make_float2(cmul, cmul), nm2 = make_float2(-m, -m);
   float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
@@ -498,10 +504,10 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<Cfg, BF16>& c, const Fw
     }
     bool ok;
     if (need_mask)
-      ok = fwd_softmax_block<Cfg, BF16, SOFTCAP, true>(c, p, s_addr, o_addr, o_full, p_full, n, lo_key - j * BN,
+      ok = fwd_softmax_block<Cfg, BF16, SOFTCAP, true>(c, p, s_addr, o_addr, o_full, p_full, n, n, lo_key - j * BN,
                                                        hi_key - j * BN, cmul, m, l, tw, tpar, turn_other);
     else
-      ok = fwd_softmax_block<Cfg, BF16, SOFTCAP, false>(c, p, s_addr, o_addr, o_full, p_full, n, 0, 0, cmul, m, l, tw,
+      ok = fwd_softmax_block<Cfg, BF16, SOFTCAP, false>(c, p, s_addr, o_addr, o_full, p_full, n, n, 0, 0, cmul, m, l, tw,
                                                         tpar, turn_other);
     if (!ok) return;
   }
@@ -552,6 +558,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(&g_device_status);
   __syncthreads();
   if (s_skip != 0) return;
+  [[maybe_unused]] const uint64_t cta_start_ns = global_timer_ns();
+  [[maybe_unused]] const long long cta_start_clk = clock64();
   B200_TL_INIT();
   if (threadIdx.x == 0) B200_TL((3 * 64 + 62) * 8 + 0);   // kernel entry
 
@@ -633,6 +641,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (threadIdx.x == 0) B200_TL((3 * 64 + 62) * 8 + 5);   // all roles done
   if (warp == 0) tmem_dealloc(c.tmem_base, Cfg::TMEM_COLS);
   B200_TL_FLUSH();
+  B200_TL_CTA(cta_start_ns, cta_start_clk, c.jmax - c.jmin);
 }
 
 // --------------------------------- host side ---------------------------------
@@ -654,6 +663,11 @@ int launch_attn_fwd_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUte
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
 }
+
+// persistent variant for head_dim 128 (attn_fwd_persist.cuh)
+template <bool BF16, bool SOFTCAP>
+int launch_attn_fwd_persist(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
+                            cudaStream_t stream);
 
 inline int attn_fwd_impl_lse_stride(const void* q, const void* k, const void* v, void* out, float* lse,
                                     int lse_stride, int batch, int q_len, int kv_len, int heads, int kv_heads,
@@ -702,9 +716,21 @@ inline int attn_fwd_impl_lse_stride(const void* q, const void* k, const void* v,
         : (cap ? launch_attn_fwd_cfg<D_, BN_, NQ_, SB_, false, true>(tq, tk, tv, p, stream)                  \
                : launch_attn_fwd_cfg<D_, BN_, NQ_, SB_, false, false>(tq, tk, tv, p, stream)))
   if (head_dim == 128) {
-    // One query tile per CTA, two CTAs per SM.  (The kernel also supports NQ = 2 -- two tiles sharing one K/V
-    // stream in a single CTA; on this part two independent CTAs per SM measured 13 % faster at seq 4096.)
+    // One query tile at a time per CTA, two CTAs per SM.  (The kernel also supports NQ = 2 -- two tiles sharing
+    // one K/V stream in a single CTA; on this part two independent CTAs per SM measured 13 % faster at seq 4096.)
+    // Default: the persistent kernel, whose CTAs walk query tiles handed out by an atomic counter.  The
+    // one-tile-per-CTA launch stays selectable for A/B timing (environment variable read once per process).
+    static const bool one_tile_per_cta = std::getenv("B200_ATTN_ONE_TILE_PER_CTA") != nullptr;
+    if (!one_tile_per_cta && B200_BN128 == 64 && B200_SB128 == 2)
+      return bf16 ? (cap ? launch_attn_fwd_persist<true, true>(tq, tk, tv, p, stream)
+                         : launch_attn_fwd_persist<true, false>(tq, tk, tv, p, stream))
+                  : (cap ? launch_attn_fwd_persist<false, true>(tq, tk, tv, p, stream)
+                         : launch_attn_fwd_persist<false, false>(tq, tk, tv, p, stream));
+#ifdef B200_NQ128
+    return B200_FWD_DISPATCH(128, B200_BN128, B200_NQ128, B200_SB128);
+#else
     return B200_FWD_DISPATCH(128, B200_BN128, 1, B200_SB128);
+#endif
   }
   return B200_FWD_DISPATCH(256, 64, 1, 2);
 #undef B200_FWD_DISPATCH

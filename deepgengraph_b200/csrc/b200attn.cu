@@ -8,6 +8,7 @@
 #include "common.cuh"
 #include "elementwise.cuh"
 #include "attn_fwd.cuh"
+#include "attn_fwd_persist.cuh"
 #include "attn_sweep.cuh"
 #include "kv_evict.cuh"
 
@@ -139,6 +140,10 @@ int b200_device_status(int* status_out) {
   if (word != 0) {
     const int zero = 0;
     B200_CUDA_TRY(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
+    // a launch that gave up may have left its tile counters mid-count
+    void* counters = nullptr;
+    B200_CUDA_TRY(cudaGetSymbolAddress(&counters, g_sched_counters));
+    B200_CUDA_TRY(cudaMemset(counters, 0, sizeof(unsigned int) * kSchedPool * 2));
   }
   *status_out = word;
   return word == 0 ? B200_OK : B200_ERR_DEVICE_TIMEOUT;
@@ -300,6 +305,11 @@ int b200_debug_set_timeline(void* buffer, int block) {
   long long* p = (long long*)buffer;
   B200_CUDA_TRY(cudaMemcpyToSymbol(g_timeline, &p, sizeof(p)));
   B200_CUDA_TRY(cudaMemcpyToSymbol(g_timeline_block, &block, sizeof(int)));
+  return B200_OK;
+}
+int b200_debug_set_cta_times(void* buffer) {
+  long long* p = (long long*)buffer;
+  B200_CUDA_TRY(cudaMemcpyToSymbol(g_cta_times, &p, sizeof(p)));
   return B200_OK;
 }
 #endif

@@ -10,6 +10,8 @@
 #include <stdint.h>
 
 #include <algorithm>
+#include <cstdlib>
+#include <mutex>
 
 #include "../../include/b200attn.h"
 
@@ -41,6 +43,7 @@ __device__ int g_device_status = 0;
 #ifdef B200_TIMELINE
 __device__ long long* g_timeline = nullptr;
 __device__ int g_timeline_block = 0;
+__device__ long long* g_cta_times = nullptr;   // [num CTAs][8]: start ns, end ns, SM id, key blocks, SM clocks
 constexpr int kTimelineSlots = 2048;
 __shared__ unsigned int s_timeline[kTimelineSlots];   // stamps stay in shared memory until the CTA ends
 __device__ __forceinline__ unsigned int clock32() {
@@ -60,7 +63,21 @@ __device__ __forceinline__ unsigned int clock32() {
         (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) == g_timeline_block)        \
       for (int _i = threadIdx.x; _i < kTimelineSlots; _i += blockDim.x) g_timeline[_i] = s_timeline[_i];  \
   } while (0)
+#define B200_TL_CTA(start_ns, start_clk, nblocks)                                                              \
+  do {                                                                                              \
+    if (g_cta_times != nullptr && threadIdx.x == 0) {                                               \
+      const long long _id = blockIdx.x + gridDim.x * (blockIdx.y + (long long)gridDim.y * blockIdx.z); \
+      unsigned _sm;                                                                                 \
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(_sm));                                              \
+      g_cta_times[_id * 8 + 0] = (long long)(start_ns);                                             \
+      g_cta_times[_id * 8 + 1] = (long long)global_timer_ns();                                      \
+      g_cta_times[_id * 8 + 2] = _sm;                                                               \
+      g_cta_times[_id * 8 + 3] = (nblocks);                                                         \
+      g_cta_times[_id * 8 + 4] = clock64() - (long long)(start_clk);                                \
+    }                                                                                               \
+  } while (0)
 #else
+#define B200_TL_CTA(start_ns, start_clk, nblocks) do { } while (0)
 #define B200_TL_INIT() do { } while (0)
 #define B200_TL(slot) do { } while (0)
 #define B200_TL_FLUSH() do { } while (0)
@@ -84,7 +101,9 @@ enum WaitCode : int {
   WAIT_N_EMPTY = 14,
   WAIT_DRAIN = 15,
   WAIT_TURN = 16,     // exp-phase turn-taking between the two query tiles
-  WAIT_SELFTEST = 17  // b200_selftest_bounded_wait
+  WAIT_SELFTEST = 17, // b200_selftest_bounded_wait
+  WAIT_SCHED = 18,    // persistent attention: next tile descriptor
+  WAIT_Q_FREE = 19    // persistent attention: Q buffer released by the previous tile
 };
 
 // ---------------------------------------------------------------------------
@@ -134,6 +153,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Non-blocking probe (try_wait may suspend the thread for a while when the phase is still open).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)

@@ -142,6 +142,41 @@ def test_full_size_config2_properties(cuda_device):
   torch.testing.assert_close(o2, 2 * o1, rtol=2e-2, atol=2e-2)
 
 
+def test_more_tiles_than_resident_ctas(cuda_device):
+  # head_dim 128 runs a persistent grid (2 CTAs per SM) whose CTAs walk several query tiles each: 2 x 10 x 20 = 400
+  # tiles is more than any B200 holds at once, so barrier phases, the K/V ring and the TMEM buffers carry over
+  # from tile to tile inside a CTA.
+  q, k, v = _qkv(2, 2560, 2560, 10, 10, 128, torch.bfloat16, seed=21)
+  ref = rm.attention_ref(q, k, v, causal=True, head_chunk=5)["out"]
+  out = att.attn_fwd(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device))
+  torch.testing.assert_close(out.float().cpu(), ref, **TOL)
+
+
+def test_many_ragged_tiles_gqa_window_softcap(cuda_device):
+  # 24 heads x 16 ragged query tiles (q_len not a multiple of 128, kv_len > q_len), grouped K/V heads, sliding
+  # window and soft-cap together, again more tiles than resident CTAs
+  q, k, v = _qkv(1, 2000, 2304, 24, 8, 128, torch.float16, seed=22, q_scale=2.0)
+  ref = rm.attention_ref(q, k, v, causal=True, window=700, softcap=30.0, head_chunk=6)["out"]
+  out = att.attn_fwd(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), causal=True, window=700, softcap=30.0)
+  torch.testing.assert_close(out.float().cpu(), ref, **TOL)
+
+
+def test_launches_on_two_streams_interleave(cuda_device):
+  # every launch takes its own tile counter; launches in flight on different streams must not share one
+  q, k, v = (t.to(cuda_device) for t in _qkv(2, 1536, 1536, 16, 16, 128, torch.bfloat16, seed=23))
+  want = att.attn_fwd(q, k, v)
+  torch.cuda.synchronize()
+  streams = [torch.cuda.Stream(device=cuda_device) for _ in range(2)]
+  outs = []
+  for rep in range(4):
+    for st in streams:
+      with torch.cuda.stream(st):
+        outs.append(att.attn_fwd(q, k, v))
+  torch.cuda.synchronize()
+  for o in outs:
+    assert torch.equal(o, want)
+
+
 def test_host_validation(cuda_device):
   q, k, v = (t.to(cuda_device) for t in _qkv(1, 128, 128, 2, 2, 128, torch.bfloat16))
   with pytest.raises(TypeError):
