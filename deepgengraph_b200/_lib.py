@@ -33,6 +33,8 @@ SIGNATURES = {
     "b200_gelu_tanh_and_mul": (_i, [_vp, _vp, _i64, _i, _i, _vp]),
     "b200_rotary_embedding_online": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i64, _i64, _f, _i, _vp]),
     "b200_attn_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]),
+    "b200_attn_fwd_strided": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64,
+                                   _i, _i, _f, _f, _vp]),
     "b200_attn_score_workspace_bytes": (_i64, [_i, _i, _i, _i]),
     "b200_attn_score": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]),
     "b200_attn_score_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]),

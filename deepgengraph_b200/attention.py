@@ -22,7 +22,16 @@ from . import _lib
 from .native_ops import _dtype_code, _require_cuda, _stream_ptr
 
 
-def _check_qkv(where, q, k, v):
+def _row_strided(t):
+  """True for a [B, S, H, D] view whose heads are packed (stride D) inside token rows that may be wider than
+  H * D -- e.g. the q / k / v slices of a fused QKV projection output."""
+  B, S, H, D = t.shape
+  sb, ss, sh, sd = t.stride()
+  return (sd == 1 and sh == D and ss >= H * D and ss % 8 == 0 and (B == 1 or (sb >= S * ss and sb % 8 == 0))
+          and t.data_ptr() % 16 == 0)
+
+
+def _check_qkv(where, q, k, v, allow_row_strided=False):
   dev = _require_cuda(where, q, k, v)
   if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
     raise ValueError(f"{where}: q, k, v must be [batch, seq, heads, head_dim]")
@@ -33,24 +42,36 @@ def _check_qkv(where, q, k, v):
   if q.size(2) % k.size(2) != 0:
     raise ValueError(f"{where}: heads ({q.size(2)}) not a multiple of kv heads ({k.size(2)})")
   if not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()):
-    raise ValueError(f"{where}: q, k, v must be contiguous")
+    if not (allow_row_strided and _row_strided(q) and _row_strided(k) and _row_strided(v)):
+      raise ValueError(f"{where}: q, k, v must be contiguous" +
+                       (" or row-strided views (packed heads, 16-byte aligned strides)" if allow_row_strided else ""))
   return dev
 
 
 def _attn_fwd_impl(q, k, v, causal, window, softcap, scale, want_lse=False):
   where = "attn_fwd"
-  dev = _check_qkv(where, q, k, v)
+  dev = _check_qkv(where, q, k, v, allow_row_strided=True)
   B, Sq, H, D = q.shape
   Skv, Hk = k.size(1), k.size(2)
   if scale is None or scale <= 0:
     scale = 1.0 / math.sqrt(D)
-  out = torch.empty_like(q)
+  out = torch.empty((B, Sq, H, D), dtype=q.dtype, device=dev)
   lse = torch.empty((B, H, Sq), dtype=torch.float32, device=dev) if want_lse else None
   with torch.cuda.device(dev):
-    st = _lib.load().b200_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
-                                   lse.data_ptr() if want_lse else None, B, Sq, Skv, H, Hk, D,
-                                   _dtype_code(q, where), int(bool(causal)), int(window), float(softcap),
-                                   float(scale), _stream_ptr(dev))
+    if q.is_contiguous() and k.is_contiguous() and v.is_contiguous():
+      st = _lib.load().b200_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                     lse.data_ptr() if want_lse else None, B, Sq, Skv, H, Hk, D,
+                                     _dtype_code(q, where), int(bool(causal)), int(window), float(softcap),
+                                     float(scale), _stream_ptr(dev))
+    else:
+      # views into a wider buffer (fused QKV projection output): no copy, the strides go to the TMA descriptors
+      def strides(t):
+        return t.stride(1), (t.stride(0) if t.size(0) > 1 else t.size(1) * t.stride(1))
+      (qt, qb), (kt, kb), (vt, vb) = strides(q), strides(k), strides(v)
+      st = _lib.load().b200_attn_fwd_strided(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                             lse.data_ptr() if want_lse else None, B, Sq, Skv, H, Hk, D,
+                                             _dtype_code(q, where), qt, qb, kt, kb, vt, vb, int(bool(causal)),
+                                             int(window), float(softcap), float(scale), _stream_ptr(dev))
   _lib.check(st, where)
   return (out, lse) if want_lse else out
 

@@ -669,10 +669,15 @@ template <bool BF16, bool SOFTCAP>
 int launch_attn_fwd_persist(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
                             cudaStream_t stream);
 
+// element strides of q / k / v when they are views into a larger buffer (0 = contiguous)
+struct AttnStrides {
+  int64_t q_token, q_batch, k_token, k_batch, v_token, v_batch;
+};
+
 inline int attn_fwd_impl_lse_stride(const void* q, const void* k, const void* v, void* out, float* lse,
                                     int lse_stride, int batch, int q_len, int kv_len, int heads, int kv_heads,
                                     int head_dim, int dtype, int causal, int window, float softcap, float scale,
-                                    cudaStream_t stream) {
+                                    cudaStream_t stream, const AttnStrides* strides = nullptr) {
   if (!q || !k || !v || !out) return B200_ERR_BAD_ARGUMENT;
   if (batch <= 0 || q_len <= 0 || kv_len <= 0 || heads <= 0 || kv_heads <= 0) return B200_ERR_BAD_ARGUMENT;
   if (dtype != B200_F16 && dtype != B200_BF16) return B200_ERR_BAD_DTYPE;
@@ -688,9 +693,14 @@ inline int attn_fwd_impl_lse_stride(const void* q, const void* k, const void* v,
   const int bn = head_dim == 128 ? B200_BN128 : 64;
   CUtensorMap tq, tk, tv;
   int rc;
-  if ((rc = make_bshd_tensor_map(&tq, q, batch, q_len, heads, head_dim, 128, bf16)) != B200_OK) return rc;
-  if ((rc = make_bshd_tensor_map(&tk, k, batch, kv_len, kv_heads, head_dim, bn, bf16)) != B200_OK) return rc;
-  if ((rc = make_bshd_tensor_map(&tv, v, batch, kv_len, kv_heads, head_dim, bn, bf16)) != B200_OK) return rc;
+  const AttnStrides contiguous{0, 0, 0, 0, 0, 0};
+  const AttnStrides& st = strides ? *strides : contiguous;
+  if ((rc = make_bshd_tensor_map(&tq, q, batch, q_len, heads, head_dim, 128, bf16, st.q_token, st.q_batch)) != B200_OK)
+    return rc;
+  if ((rc = make_bshd_tensor_map(&tk, k, batch, kv_len, kv_heads, head_dim, bn, bf16, st.k_token, st.k_batch)) != B200_OK)
+    return rc;
+  if ((rc = make_bshd_tensor_map(&tv, v, batch, kv_len, kv_heads, head_dim, bn, bf16, st.v_token, st.v_batch)) != B200_OK)
+    return rc;
 
   FwdParams p;
   p.out = out;

@@ -28,13 +28,15 @@ EncodeTiledFn get_encode_tiled() {
   return fn;
 }
 
+// token_stride / batch_stride in elements; 0 = contiguous [batch, seq, heads, dim]
 int make_bshd_tensor_map(CUtensorMap* map, const void* base, int batch, int seq, int heads, int dim, int box_rows,
-                         bool bf16) {
+                         bool bf16, int64_t token_stride, int64_t batch_stride) {
   EncodeTiledFn enc = get_encode_tiled();
   if (!enc) return B200_ERR_CUDA;
+  if (token_stride == 0) token_stride = (int64_t)heads * dim;
+  if (batch_stride == 0) batch_stride = (int64_t)seq * token_stride;
   const cuuint64_t dims[4] = {(cuuint64_t)dim, (cuuint64_t)heads, (cuuint64_t)seq, (cuuint64_t)batch};
-  const cuuint64_t strides[3] = {(cuuint64_t)dim * 2, (cuuint64_t)heads * dim * 2,
-                                 (cuuint64_t)seq * heads * dim * 2};
+  const cuuint64_t strides[3] = {(cuuint64_t)dim * 2, (cuuint64_t)token_stride * 2, (cuuint64_t)batch_stride * 2};
   const cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
@@ -239,6 +241,23 @@ int b200_attn_fwd(const void* q, const void* k, const void* v, void* out, float*
                   float softcap, float scale, void* stream) {
   return attn_fwd_impl(q, k, v, out, lse, batch, q_len, kv_len, heads, kv_heads, head_dim, dtype, causal, window,
                        softcap, scale, (cudaStream_t)stream);
+}
+
+int b200_attn_fwd_strided(const void* q, const void* k, const void* v, void* out, float* lse, int batch, int q_len,
+                          int kv_len, int heads, int kv_heads, int head_dim, int dtype, int64_t q_token_stride,
+                          int64_t q_batch_stride, int64_t k_token_stride, int64_t k_batch_stride,
+                          int64_t v_token_stride, int64_t v_batch_stride, int causal, int window, float softcap,
+                          float scale, void* stream) {
+  const int64_t st[6] = {q_token_stride, q_batch_stride, k_token_stride, k_batch_stride, v_token_stride, v_batch_stride};
+  const int64_t row[6] = {(int64_t)heads * head_dim, 0, (int64_t)kv_heads * head_dim, 0, (int64_t)kv_heads * head_dim, 0};
+  const int64_t len[6] = {0, q_len, 0, kv_len, 0, kv_len};
+  for (int i = 0; i < 6; i += 2) {
+    if (st[i] < row[i] || st[i + 1] < st[i] * len[i + 1]) return B200_ERR_BAD_ARGUMENT;   // overlapping rows / batches
+    if (st[i] % 8 != 0 || st[i + 1] % 8 != 0) return B200_ERR_MISALIGNED;                 // TMA: 16-byte strides
+  }
+  AttnStrides strides{q_token_stride, q_batch_stride, k_token_stride, k_batch_stride, v_token_stride, v_batch_stride};
+  return attn_fwd_impl_lse_stride(q, k, v, out, lse, q_len, batch, q_len, kv_len, heads, kv_heads, head_dim, dtype,
+                                  causal, window, softcap, scale, (cudaStream_t)stream, &strides);
 }
 
 int64_t b200_attn_score_workspace_bytes(int batch, int q_len, int kv_len, int heads) {

@@ -481,7 +481,7 @@ EncodeTiledFn get_encode_tiled();
 // BSHD tensor [batch, seq, heads, dim] of 16-bit elements, box = (64 dims, 1 head, box_rows rows, 1 batch),
 // 128-byte swizzle.  Returns a b200_status.
 int make_bshd_tensor_map(CUtensorMap* map, const void* base, int batch, int seq, int heads, int dim, int box_rows,
-                         bool bf16);
+                         bool bf16, int64_t token_stride = 0, int64_t batch_stride = 0);
 // Row-major float32 matrix [rows, cols], box = (box_cols, box_rows); swizzle128 selects the 128-byte swizzle
 // (box_cols must then be 32).
 int make_f32_matrix_tensor_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int box_rows,

@@ -54,9 +54,13 @@ def gemma2_layer(x, w, cfg, positions=None):
   if positions is None:
     positions = torch.arange(S, dtype=torch.int32, device=x.device).repeat(B)
   _ops.rotary_embedding_online(positions, qkv[:, :H * D], qkv[:, H * D:(H + Hk) * D], D, cfg.rope_theta)
-  q = qkv[:, :H * D].reshape(B, S, H, D).contiguous()
-  k = qkv[:, H * D:(H + Hk) * D].reshape(B, S, Hk, D).contiguous()
-  v = qkv[:, (H + Hk) * D:].reshape(B, S, Hk, D).contiguous()
+  # q / k / v stay views of the projection output (no split copies; the reference makes three,
+  # models/attn.py:37-40, and synchronises the device, :43): the attention kernel reads them through strided
+  # TMA descriptors
+  qkv3 = qkv.view(B, S, (H + 2 * Hk) * D)
+  q = qkv3[:, :, :H * D].unflatten(-1, (H, D))
+  k = qkv3[:, :, H * D:(H + Hk) * D].unflatten(-1, (Hk, D))
+  v = qkv3[:, :, (H + Hk) * D:].unflatten(-1, (Hk, D))
   a = _att.attn_fwd(q, k, v, causal=True, window=cfg.window, softcap=cfg.softcap)
   o = torch.matmul(a.reshape(T, H * D), w["o"].t())                    # attention block output
   # residual add fused with the second norm: res <- x + o (in place in `res`), o <- rms_norm(res)

@@ -119,6 +119,24 @@ int b200_attn_fwd(const void* q, const void* k, const void* v, void* out, float*
                   int batch, int q_len, int kv_len, int heads, int kv_heads, int head_dim,
                   int dtype, int causal, int window, float softcap, float scale, void* stream);
 
+/*
+ * b200_attn_fwd for q / k / v that are VIEWS into a larger buffer -- typically the [tokens, (heads + 2 kv_heads) *
+ * head_dim] output of the fused QKV projection, rotated in place by b200_rotary_embedding_online.  Replaces the
+ * split -> contiguous x 3 -> view sequence of the reference's model glue
+ * (deepgengraph_exp/cases/models/attn.py:36-42, models/h2o.py / roco.py / kf.py likewise): no copy is made, the TMA
+ * descriptors carry the strides.
+ * *_token_stride: elements between consecutive tokens (>= heads * head_dim, resp. kv_heads * head_dim);
+ * *_batch_stride: elements between batches (>= len * token stride).  Head h of a token starts h * head_dim
+ * elements into the token's row.  All strides must be multiples of 8 elements (16 bytes); `out` is contiguous
+ * [batch, q_len, heads, head_dim].
+ */
+int b200_attn_fwd_strided(const void* q, const void* k, const void* v, void* out, float* lse,
+                          int batch, int q_len, int kv_len, int heads, int kv_heads, int head_dim, int dtype,
+                          int64_t q_token_stride, int64_t q_batch_stride,
+                          int64_t k_token_stride, int64_t k_batch_stride,
+                          int64_t v_token_stride, int64_t v_batch_stride,
+                          int causal, int window, float softcap, float scale, void* stream);
+
 /* Bytes of scratch that b200_attn_score / b200_attn_kf_score need for these sizes. */
 int64_t b200_attn_score_workspace_bytes(int batch, int q_len, int kv_len, int heads);
 

@@ -177,6 +177,31 @@ def test_launches_on_two_streams_interleave(cuda_device):
     assert torch.equal(o, want)
 
 
+@pytest.mark.parametrize("D,H,Hk", [(128, 6, 2), (256, 2, 1)])
+def test_views_of_a_fused_qkv_projection_need_no_copy(cuda_device, D, H, Hk):
+  # q, k, v as slices of one [B, S, (H + 2 Hk) D] buffer (what the model glue gets from its QKV GEMM,
+  # models/attn.py:35-36): the strided entry point must give the bits of the contiguous one
+  B, S = 2, 640
+  g = torch.Generator().manual_seed(31)
+  qkv = torch.randn(B, S, (H + 2 * Hk) * D, generator=g).to(torch.bfloat16).to(cuda_device)
+  q = qkv[:, :, :H * D].unflatten(-1, (H, D))
+  k = qkv[:, :, H * D:(H + Hk) * D].unflatten(-1, (Hk, D))
+  v = qkv[:, :, (H + Hk) * D:].unflatten(-1, (Hk, D))
+  assert not q.is_contiguous() and q.data_ptr() == qkv.data_ptr()
+  got, lse = att.attn_fwd_with_lse(q, k, v, causal=True, window=300)
+  want, lse_want = att.attn_fwd_with_lse(q.contiguous(), k.contiguous(), v.contiguous(), causal=True, window=300)
+  assert got.is_contiguous() and torch.equal(got, want) and torch.equal(lse, lse_want)
+  ref = rm.attention_ref(q.cpu(), k.cpu(), v.cpu(), causal=True, window=300)["out"]
+  torch.testing.assert_close(got.float().cpu(), ref, **TOL)
+
+
+def test_views_with_unaligned_strides_are_rejected(cuda_device):
+  qkv = torch.zeros(1, 256, 3 * 128 + 4, dtype=torch.bfloat16, device=cuda_device)   # row stride not 16-byte aligned
+  q, k, v = (qkv[:, :, i * 128:(i + 1) * 128].unflatten(-1, (1, 128)) for i in range(3))
+  with pytest.raises(ValueError):
+    att.attn_fwd(q, k, v)
+
+
 def test_host_validation(cuda_device):
   q, k, v = (t.to(cuda_device) for t in _qkv(1, 128, 128, 2, 2, 128, torch.bfloat16))
   with pytest.raises(TypeError):
