@@ -41,6 +41,7 @@ SIGNATURES = {
     "b200_attn_corm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "b200_avg_pool1d_f32": (_i, [_vp, _vp, _i64, _i, _i, _vp]),
     "b200_kv_evict_topk": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "b200_kv_evict_roco": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "b200_attn_kf_score": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]),
 }
 

@@ -289,3 +289,30 @@ def kv_evict_topk(score, k, v, budget, return_indices=False):
                                         _dtype_code(k, where), _stream_ptr(dev))
   _lib.check(st, where)
   return (kv_cache, idx) if return_indices else kv_cache
+
+
+def kv_evict_roco(score, score_sq, k, v, q_len, budget, recent, return_indices=False):
+  """RoCo's KV-cache eviction (models/roco.py:52-66): keep the `recent` keys whose attention probabilities vary
+  most over the queries (largest std, from the column sums of p and p^2) and, of the rest, the `budget` keys with
+  the largest mean probability; position order.
+  score, score_sq float32 [B, H, S] (from attn_score_fwd(want_sq=True)); k, v [B, S, H, D].  Returns kv_cache
+  [B, 2, budget + recent, H, D] and, if asked, the selected positions int32 [B, H, budget + recent]."""
+  where = "kv_evict_roco"
+  dev = _require_cuda(where, score, score_sq, k, v)
+  for name, t in (("score", score), ("score_sq", score_sq)):
+    if t.dtype != torch.float32 or t.dim() != 3 or not t.is_contiguous():
+      raise ValueError(f"{where}: {name} must be contiguous float32 [batch, heads, seq]")
+  if k.dim() != 4 or k.shape != v.shape or k.dtype != v.dtype or not (k.is_contiguous() and v.is_contiguous()):
+    raise ValueError(f"{where}: k, v must be contiguous [batch, seq, heads, head_dim] of one dtype")
+  B, S, H, D = k.shape
+  if tuple(score.shape) != (B, H, S) or score_sq.shape != score.shape:
+    raise ValueError(f"{where}: score shapes {tuple(score.shape)}, {tuple(score_sq.shape)} do not match k {tuple(k.shape)}")
+  keep = int(budget) + int(recent)
+  kv_cache = torch.empty((B, 2, keep, H, D), dtype=k.dtype, device=dev)
+  idx = torch.empty((B, H, keep), dtype=torch.int32, device=dev) if return_indices else None
+  with torch.cuda.device(dev):
+    st = _lib.load().b200_kv_evict_roco(score.data_ptr(), score_sq.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                        kv_cache.data_ptr(), idx.data_ptr() if return_indices else None, B, S, H, D,
+                                        int(q_len), int(budget), int(recent), _dtype_code(k, where), _stream_ptr(dev))
+  _lib.check(st, where)
+  return (kv_cache, idx) if return_indices else kv_cache

@@ -298,6 +298,15 @@ int b200_kv_evict_topk(const float* score, const void* k, const void* v, void* k
                             (cudaStream_t)stream);
 }
 
+int b200_kv_evict_roco(const float* score, const float* score_sq, const void* k, const void* v, void* kv_cache,
+                       int32_t* indices, int batch, int seq_len, int heads, int head_dim, int q_len, int budget,
+                       int recent, int dtype, void* stream) {
+  const int elem = dtype == B200_F32 ? 4 : (dtype == B200_F16 || dtype == B200_BF16) ? 2 : 0;
+  if (elem == 0) return B200_ERR_BAD_DTYPE;
+  return kv_evict_roco_impl(score, score_sq, k, v, kv_cache, indices, batch, seq_len, heads, head_dim, q_len, budget,
+                            recent, elem, (cudaStream_t)stream);
+}
+
 int b200_attn_kf_score(const void* q, const void* k, const void* v, const float* exp_rand, void* out,
                        float* kf_score, void* workspace, int64_t workspace_bytes, int batch, int q_len, int kv_len,
                        int heads, int head_dim, int dtype, int causal, float tau, float scale, void* stream) {

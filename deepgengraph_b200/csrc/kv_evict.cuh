@@ -129,6 +129,179 @@ kv_evict_topk_kernel(const float* __restrict__ score, const uint8_t* __restrict_
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// RoCo's selection (deepgengraph_exp/cases/models/roco.py:52-66):
+//   std   = sqrt(sq / q_len - (score / q_len) ** 2)
+//   A     = the `recent` keys with the LARGEST std            (topk(std, largest=True, k=recent))
+//   B     = among the other keys, the `budget` keys with the largest score / q_len
+//   cache = K, V rows of A u B in position order              -> [B, 2, budget + recent, H, D]
+// One CTA per (batch, head): radix select on std, an ordered pass that marks A in a shared-memory byte map,
+// radix select on the mean score over the unmarked keys, one ordered compaction, gather.  The statistics are
+// recomputed from the two score vectors in every pass (L2 hits) with the reference's fp32 operation order
+// (round-to-nearest division, multiply, subtract, square root -- no contraction, no approximations), so the
+// ordering of the keys is the reference's.  NaN (variance rounded below zero) ranks above +inf, as in torch.topk.
+// ---------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t score_key_nan_high(float f) {
+  return (f != f) ? 0xffffffffu : score_key(f);
+}
+__device__ __forceinline__ float roco_mean(float score, float q_len) { return __fdiv_rn(score, q_len); }
+__device__ __forceinline__ float roco_std(float score, float sq, float q_len) {
+  const float m = __fdiv_rn(score, q_len);
+  return __fsqrt_rn(__fsub_rn(__fdiv_rn(sq, q_len), __fmul_rn(m, m)));
+}
+
+// Block-wide radix select: key value of the `want`-th largest key among the keys with use(i) true.
+// Returns the threshold; *need_equal = how many keys EQUAL to it belong to the top `want`.
+template <class KeyFn, class UseFn>
+__device__ __forceinline__ uint32_t block_radix_select(KeyFn key, UseFn use, int seq, int want, int* hist,
+                                                       uint32_t* s_prefix, int* s_remaining, int* need_equal) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    *s_prefix = 0;
+    *s_remaining = want;
+  }
+  uint32_t mask = 0;
+  for (int pass = 3; pass >= 0; --pass) {
+    for (int i = threadIdx.x; i < 256; i += kEvictThreads) hist[i] = 0;
+    __syncthreads();
+    const uint32_t prefix = *s_prefix;
+    const int shift = pass * 8;
+    for (int i = threadIdx.x; i < seq; i += kEvictThreads) {
+      if (!use(i)) continue;
+      const uint32_t u = key(i);
+      if ((u & mask) == prefix) atomicAdd(&hist[(u >> shift) & 0xff], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int remaining = *s_remaining, bin = 255;
+      for (; bin > 0; --bin) {
+        if (hist[bin] >= remaining) break;
+        remaining -= hist[bin];
+      }
+      *s_prefix = prefix | ((uint32_t)bin << shift);
+      *s_remaining = remaining;
+    }
+    mask |= 0xffu << shift;
+    __syncthreads();
+  }
+  *need_equal = *s_remaining;
+  return *s_prefix;
+}
+
+template <int ELEM_BYTES>
+__global__ void __launch_bounds__(kEvictThreads)
+kv_evict_roco_kernel(const float* __restrict__ score, const float* __restrict__ score_sq,
+                     const uint8_t* __restrict__ k, const uint8_t* __restrict__ v, uint8_t* __restrict__ kv_cache,
+                     int32_t* __restrict__ indices_out, int seq, int heads, int head_dim, float q_len, int budget,
+                     int recent) {
+  __shared__ int hist[256];
+  __shared__ int warp_sums[kEvictThreads / 32];
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_remaining;
+  extern __shared__ int32_t s_dyn[];
+  const int keep = budget + recent;
+  int32_t* s_idx = s_dyn;                                        // [keep] selected key indices, ascending
+  uint8_t* in_a = reinterpret_cast<uint8_t*>(s_dyn + keep);      // [seq] 1 = key belongs to A
+
+  const int bh = blockIdx.x, b = bh / heads, h = bh - b * heads;
+  const float* sc = score + (int64_t)bh * seq;
+  const float* sq = score_sq + (int64_t)bh * seq;
+  auto std_key = [&](int i) { return score_key_nan_high(roco_std(sc[i], sq[i], q_len)); };
+  auto mean_key = [&](int i) { return score_key_nan_high(roco_mean(sc[i], q_len)); };
+
+  // ---- A: the `recent` keys with the largest std (ties towards the lower index) ----
+  for (int i = threadIdx.x; i < seq; i += kEvictThreads) in_a[i] = 0;
+  if (recent > 0) {
+    int need_eq;
+    const uint32_t thr = block_radix_select(std_key, [](int) { return true; }, seq, recent, hist, &s_prefix,
+                                            &s_remaining, &need_eq);
+    int eq_base = 0;
+    for (int i0 = 0; i0 < seq; i0 += kEvictThreads) {
+      const int i = i0 + threadIdx.x;
+      const uint32_t u = i < seq ? std_key(i) : 0u;
+      const int is_eq = (i < seq && u == thr) ? 1 : 0;
+      int eq_total;
+      const int eq_before = eq_base + block_exclusive_scan(is_eq, warp_sums, &eq_total);
+      if (i < seq && (u > thr || (is_eq && eq_before < need_eq))) in_a[i] = 1;
+      eq_base += eq_total;
+    }
+  }
+  __syncthreads();
+
+  // ---- B: among the other keys, the `budget` keys with the largest mean score ----
+  int need_eq_b = 0;
+  uint32_t thr_b = 0xffffffffu;
+  if (budget > 0)
+    thr_b = block_radix_select(mean_key, [&](int i) { return in_a[i] == 0; }, seq, budget, hist, &s_prefix,
+                               &s_remaining, &need_eq_b);
+
+  // ---- ordered compaction of A u B ----
+  int sel_base = 0, eq_base = 0;
+  for (int i0 = 0; i0 < seq; i0 += kEvictThreads) {
+    const int i = i0 + threadIdx.x;
+    const bool a = i < seq && in_a[i] != 0;
+    const uint32_t u = (i < seq && !a && budget > 0) ? mean_key(i) : 0u;
+    const int is_eq = (i < seq && !a && budget > 0 && u == thr_b) ? 1 : 0;
+    int eq_total, sel_total;
+    const int eq_before = eq_base + block_exclusive_scan(is_eq, warp_sums, &eq_total);
+    const bool in_b = i < seq && !a && budget > 0 && (u > thr_b || (is_eq && eq_before < need_eq_b));
+    const int is_sel = (a || in_b) ? 1 : 0;
+    const int pos = sel_base + block_exclusive_scan(is_sel, warp_sums, &sel_total);
+    if (is_sel && pos < keep) s_idx[pos] = i;
+    sel_base += sel_total;
+    eq_base += eq_total;
+  }
+  __syncthreads();
+
+  if (indices_out != nullptr)
+    for (int i = threadIdx.x; i < keep; i += kEvictThreads) indices_out[(int64_t)bh * keep + i] = s_idx[i];
+
+  // ---- gather (layout as kv_evict_topk_kernel) ----
+  const int row_bytes = head_dim * ELEM_BYTES;
+  const int vec_per_row = row_bytes / 16;
+  const int64_t src_row_stride = (int64_t)heads * row_bytes;
+  const int64_t src_batch = (int64_t)b * seq * src_row_stride + (int64_t)h * row_bytes;
+  const int64_t dst_plane = (int64_t)keep * heads * row_bytes;
+  const int64_t dst_batch = (int64_t)b * 2 * dst_plane + (int64_t)h * row_bytes;
+  const int total = keep * vec_per_row;
+  for (int g = threadIdx.x; g < total; g += kEvictThreads) {
+    const int r = g / vec_per_row, c = g - r * vec_per_row;
+    const int64_t src = src_batch + (int64_t)s_idx[r] * src_row_stride + c * 16;
+    const int64_t dst = dst_batch + (int64_t)r * src_row_stride + c * 16;
+    *reinterpret_cast<uint4*>(kv_cache + dst) = *reinterpret_cast<const uint4*>(k + src);
+    *reinterpret_cast<uint4*>(kv_cache + dst + dst_plane) = *reinterpret_cast<const uint4*>(v + src);
+  }
+}
+
+inline int kv_evict_roco_impl(const float* score, const float* score_sq, const void* k, const void* v,
+                              void* kv_cache, int32_t* indices, int batch, int seq, int heads, int head_dim,
+                              int q_len, int budget, int recent, int elem_bytes, cudaStream_t stream) {
+  if (!score || !score_sq || !k || !v || !kv_cache) return B200_ERR_BAD_ARGUMENT;
+  if (batch <= 0 || seq <= 0 || heads <= 0 || head_dim <= 0 || q_len <= 0) return B200_ERR_BAD_ARGUMENT;
+  if (budget < 0 || recent < 0 || budget + recent <= 0 || budget + recent > seq) return B200_ERR_BAD_ARGUMENT;
+  if (elem_bytes != 2 && elem_bytes != 4) return B200_ERR_BAD_DTYPE;
+  if ((head_dim * elem_bytes) % 16 != 0 || !aligned16(k) || !aligned16(v) || !aligned16(kv_cache))
+    return B200_ERR_MISALIGNED;
+  const size_t smem = (size_t)(budget + recent) * sizeof(int32_t) + (size_t)((seq + 15) / 16) * 16;
+  if (smem > 200 * 1024) return B200_ERR_UNSUPPORTED;
+  const int grid = batch * heads;
+  auto launch = [&](auto kern) -> int {
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    B200_CUDA_TRY(cudaGetDevice(&dev));
+    if (smem > 48 * 1024 && configured_dev != dev) {
+      B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      configured_dev = dev;
+    }
+    kern<<<grid, kEvictThreads, smem, stream>>>(score, score_sq, (const uint8_t*)k, (const uint8_t*)v,
+                                                (uint8_t*)kv_cache, indices, seq, heads, head_dim, (float)q_len,
+                                                budget, recent);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+  };
+  return elem_bytes == 2 ? launch(kv_evict_roco_kernel<2>) : launch(kv_evict_roco_kernel<4>);
+}
+
 inline int kv_evict_topk_impl(const float* score, const void* k, const void* v, void* kv_cache, int32_t* indices,
                               int batch, int seq, int heads, int head_dim, int budget, int elem_bytes,
                               cudaStream_t stream) {

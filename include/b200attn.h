@@ -208,6 +208,22 @@ int b200_kv_evict_topk(const float* score, const void* k, const void* v, void* k
                        int batch, int seq_len, int heads, int head_dim, int budget, int dtype, void* stream);
 
 /*
+ * RoCo's KV-cache eviction -- deepgengraph_exp/cases/models/roco.py:52-66:
+ *   std = sqrt(score_sq / q_len - (score / q_len)^2)                (fp32, the reference's operation order)
+ *   A   = the `recent` keys with the largest std                    (roco.py:55, topk(std, largest=True))
+ *   B   = among the other keys, the `budget` keys with the largest score / q_len   (roco.py:54,56-57)
+ *   kv_cache = rows of A u B in ascending key order                 (roco.py:58-65)
+ * score, score_sq  float32 [batch, heads, seq_len]  (column sums of p and p^2 from b200_attn_score)
+ * k, v             [batch, seq_len, heads, head_dim]
+ * kv_cache         [batch, 2, budget + recent, heads, head_dim]
+ * indices          int32 [batch, heads, budget + recent], optional (may be NULL)
+ * Ties keep the lower key index; a NaN std (variance rounded below zero) ranks highest, as in torch.topk.
+ */
+int b200_kv_evict_roco(const float* score, const float* score_sq, const void* k, const void* v, void* kv_cache,
+                       int32_t* indices, int batch, int seq_len, int heads, int head_dim, int q_len, int budget,
+                       int recent, int dtype, void* stream);
+
+/*
  * KeyFormer: attention output plus
  *   kf_score[b, h, j] = sum_i softmax_j((logit_ij - log(exp_rand_ij)) / tau)
  *   -- KeyFormer.forward kernels/kf.py:19-42

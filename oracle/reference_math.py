@@ -119,6 +119,26 @@ def kv_evict_topk_ref(score, k, v, budget):
   return torch.cat([k_cache, v_cache], dim=1), sel
 
 
+def kv_evict_roco_ref(score, score_sq, k, v, q_len, budget, recent):
+  """RoCo's KV-cache eviction, the reference's own sequence of torch calls
+  (deepgengraph_exp/cases/models/roco.py:52-66): std from the two column sums, the `recent` keys of largest std are
+  always kept, of the others the `budget` keys of largest mean score; sorted, gathered, concatenated.
+  score, score_sq [B, H, S] fp32; k/v [B, S, H, D].  Returns (kv_cache [B, 2, budget + recent, H, D],
+  sorted indices [B, H, budget + recent])."""
+  B, S, H, D = k.shape
+  std = torch.sqrt(score_sq / q_len - (score / q_len) ** 2)
+  _, other = torch.topk(std, largest=False, k=S - recent, dim=-1)
+  _, rec = torch.topk(std, largest=True, k=recent, dim=-1)
+  _, sel_in_other = torch.topk(score.gather(dim=-1, index=other) / q_len, dim=-1, k=budget)
+  sel = other.gather(dim=-1, index=sel_in_other)
+  sel = torch.cat([sel, rec], dim=-1).sort(dim=-1)[0]                  # [B, H, budget + recent]
+  keep = budget + recent
+  index = sel.transpose(1, 2)[:, :, :, None].expand(B, keep, H, D)
+  k_cache = torch.gather(k, dim=1, index=index).view(B, 1, keep, H, D)
+  v_cache = torch.gather(v, dim=1, index=index).view(B, 1, keep, H, D)
+  return torch.cat([k_cache, v_cache], dim=1), sel
+
+
 # --------------------------------------------------------------------------------------------
 # csrc/ ops.  Semantic truth = the CUDA sources (csrc/norm.cu, activation.cu, pos_encoding.cu);
 # the Python stand-ins in deepgengraph_exp/cases/models/llama_base.py discard their results.

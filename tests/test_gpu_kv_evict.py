@@ -44,3 +44,40 @@ def test_scores_from_the_fused_kernel_and_ties(cuda_device):
   kk = torch.randn(1, 8, 1, 128, device=cuda_device, dtype=torch.bfloat16)
   _, idx = att.kv_evict_topk(sc, kk, kk, 3, return_indices=True)
   assert idx.cpu().tolist() == [[[3, 5, 7]]]
+
+
+def _roco_stats(B, H, Sq, S, seed):
+  g = torch.Generator().manual_seed(seed)
+  logits = torch.randn(B, H, Sq, S, generator=g) * 2
+  mask = torch.triu(torch.full((Sq, S), float("-inf")), diagonal=S - Sq + 1)
+  p = torch.softmax(logits + mask, dim=-1)
+  return p.sum(dim=2).contiguous(), (p * p).sum(dim=2).contiguous()
+
+
+@pytest.mark.parametrize("shape,budget,recent", [((1, 2048, 4, 128), 512, 32), ((2, 1000, 3, 128), 100, 1),
+                                                  ((1, 777, 2, 64), 0, 50), ((1, 640, 2, 256), 600, 40),
+                                                  ((1, 512, 2, 128), 64, 0)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_roco_selection_matches_the_reference_sequence(cuda_device, shape, budget, recent, dtype):
+  B, S, H, D = shape
+  score, score_sq = _roco_stats(B, H, S, S, seed=S + budget)
+  g = torch.Generator().manual_seed(recent)
+  k = torch.randn(B, S, H, D, generator=g).to(dtype)
+  v = torch.randn(B, S, H, D, generator=g).to(dtype)
+  ref_cache, ref_idx = rm.kv_evict_roco_ref(score, score_sq, k, v, S, budget, recent)
+  cache, idx = att.kv_evict_roco(score.to(cuda_device), score_sq.to(cuda_device), k.to(cuda_device),
+                                 v.to(cuda_device), S, budget, recent, return_indices=True)
+  assert torch.equal(idx.cpu().long(), ref_idx)
+  assert torch.equal(cache.cpu(), ref_cache)
+
+
+def test_roco_end_to_end_with_the_fused_scores(cuda_device):
+  # column sums of p and p^2 from the fused kernel feed the selection, as in models/roco.py:45-66
+  g = torch.Generator().manual_seed(5)
+  q, k, v = (torch.randn(1, 1024, 2, 128, generator=g).to(torch.bfloat16).to(cuda_device) for _ in range(3))
+  _, score, score_sq = att.attn_score_fwd(q, k, v, want_sq=True)
+  cache, idx = att.kv_evict_roco(score, score_sq, k, v, 1024, 256, 32, return_indices=True)
+  ref_cache, ref_idx = rm.kv_evict_roco_ref(score.cpu(), score_sq.cpu(), k.cpu(), v.cpu(), 1024, 256, 32)
+  assert torch.equal(idx.cpu().long(), ref_idx) and torch.equal(cache.cpu(), ref_cache)
+  with pytest.raises(RuntimeError):
+    att.kv_evict_roco(score, score_sq, k, v, 1024, 1000, 100)      # keeps more keys than there are
