@@ -665,7 +665,7 @@ int launch_attn_fwd_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUte
 }
 
 // persistent variant for head_dim 128 (attn_fwd_persist.cuh)
-template <bool BF16, bool SOFTCAP>
+template <int D_, bool BF16, bool SOFTCAP>
 int launch_attn_fwd_persist(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
                             cudaStream_t stream);
 
@@ -725,24 +725,27 @@ inline int attn_fwd_impl_lse_stride(const void* q, const void* k, const void* v,
                : launch_attn_fwd_cfg<D_, BN_, NQ_, SB_, true, false>(tq, tk, tv, p, stream))                 \
         : (cap ? launch_attn_fwd_cfg<D_, BN_, NQ_, SB_, false, true>(tq, tk, tv, p, stream)                  \
                : launch_attn_fwd_cfg<D_, BN_, NQ_, SB_, false, false>(tq, tk, tv, p, stream)))
+  // Default: the persistent kernel, whose CTAs walk query tiles handed out by an atomic counter (two CTAs per SM
+  // at head_dim 128, one at 256).  The one-tile-per-CTA launch stays selectable for A/B timing (environment
+  // variable read once per process).  (That kernel also supports NQ = 2 -- two tiles sharing one K/V stream in a
+  // single CTA; at head_dim 128 two independent CTAs per SM measured 13 % faster at seq 4096.)
+  static const bool one_tile_per_cta = std::getenv("B200_ATTN_ONE_TILE_PER_CTA") != nullptr;
+#define B200_PERSIST_DISPATCH(D_)                                                                    \
+  (bf16 ? (cap ? launch_attn_fwd_persist<D_, true, true>(tq, tk, tv, p, stream)                       \
+               : launch_attn_fwd_persist<D_, true, false>(tq, tk, tv, p, stream))                     \
+        : (cap ? launch_attn_fwd_persist<D_, false, true>(tq, tk, tv, p, stream)                      \
+               : launch_attn_fwd_persist<D_, false, false>(tq, tk, tv, p, stream)))
   if (head_dim == 128) {
-    // One query tile at a time per CTA, two CTAs per SM.  (The kernel also supports NQ = 2 -- two tiles sharing
-    // one K/V stream in a single CTA; on this part two independent CTAs per SM measured 13 % faster at seq 4096.)
-    // Default: the persistent kernel, whose CTAs walk query tiles handed out by an atomic counter.  The
-    // one-tile-per-CTA launch stays selectable for A/B timing (environment variable read once per process).
-    static const bool one_tile_per_cta = std::getenv("B200_ATTN_ONE_TILE_PER_CTA") != nullptr;
-    if (!one_tile_per_cta && B200_BN128 == 64 && B200_SB128 == 2)
-      return bf16 ? (cap ? launch_attn_fwd_persist<true, true>(tq, tk, tv, p, stream)
-                         : launch_attn_fwd_persist<true, false>(tq, tk, tv, p, stream))
-                  : (cap ? launch_attn_fwd_persist<false, true>(tq, tk, tv, p, stream)
-                         : launch_attn_fwd_persist<false, false>(tq, tk, tv, p, stream));
+    if (!one_tile_per_cta && B200_BN128 == 64 && B200_SB128 == 2) return B200_PERSIST_DISPATCH(128);
 #ifdef B200_NQ128
     return B200_FWD_DISPATCH(128, B200_BN128, B200_NQ128, B200_SB128);
 #else
     return B200_FWD_DISPATCH(128, B200_BN128, 1, B200_SB128);
 #endif
   }
+  if (!one_tile_per_cta) return B200_PERSIST_DISPATCH(256);
   return B200_FWD_DISPATCH(256, 64, 1, 2);
+#undef B200_PERSIST_DISPATCH
 #undef B200_FWD_DISPATCH
 }
 

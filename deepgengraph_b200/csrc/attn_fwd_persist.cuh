@@ -1,13 +1,13 @@
-// Persistent variant of the attention forward kernel for head_dim 128.
+// Persistent variant of the attention forward kernel (head_dim 128: two CTAs per SM; head_dim 256: one).
 //
-// Same tiling, TMEM plan and warp roles as attn_fwd_kernel<128, 64, 1, 2> (one 128-row query tile at a time, two
-// S buffers, two CTAs per SM), but the grid is 2 x #SM CTAs that each walk a sequence of query tiles:
-//   * tiles are handed out by an atomic counter in head-major, heaviest-tile-first order (the K/V of ~9 heads stay
-//     L2-resident, as with the hardware's block scheduler), so the SMs drain evenly;
+// Same tiling, TMEM plan and warp roles as attn_fwd_kernel<D, 64, 1, 2> (one 128-row query tile at a time, two
+// S buffers), but the grid is CTAS_PER_SM x #SM CTAs that each walk a sequence of query tiles:
+//   * tiles are handed out by an atomic counter, (batch, head) units in L2-sized groups and tile-major,
+//     heaviest tile first inside a group (see decode_item), so the SMs drain evenly;
 //   * every barrier, the K/V ring and the TMEM buffers run continuously across tile boundaries (phases follow
 //     CTA-global counters), so the next tile's Q/K loads and its first S = Q K^T MMAs overlap the current tile's
-//     last softmax blocks and its epilogue.  A non-persistent launch pays ~6 us of un-overlapped set-up,
-//     pipeline fill and epilogue per tile and leaves the slot idle between CTAs.
+//     epilogue.  A non-persistent launch pays ~6 us of un-overlapped set-up, pipeline fill and epilogue per
+//     tile and leaves the slot idle between CTAs.
 // Per-CTA roles: warps 0-3 softmax warpgroup, warp 4 TMA producer + tile scheduler, warp 5 MMA issuer.
 #pragma once
 
@@ -55,8 +55,9 @@ __device__ __forceinline__ TileInfo decode_item(int item, const FwdParams& p, co
   return t;
 }
 
-struct PersistCfg : FwdCfg<128, 64, 1, 2> {
-  using Base = FwdCfg<128, 64, 1, 2>;
+template <int D_>
+struct PersistCfg : FwdCfg<D_, 64, 1, 2> {
+  using Base = FwdCfg<D_, 64, 1, 2>;
   static constexpr int BAR_SCHED = Base::NUM_BARS;        // [2] tile descriptor slot k % 2 published
   static constexpr int BAR_Q_FREE = BAR_SCHED + 2;        // last S MMA of a tile retired: Q buffer reusable
   static constexpr int NUM_BARS_P = BAR_Q_FREE + 1;
@@ -64,11 +65,11 @@ struct PersistCfg : FwdCfg<128, 64, 1, 2> {
   static_assert(SMEM_BYTES_P <= Base::SMEM_BUDGET, "shared memory budget exceeded");
 };
 
-template <bool BF16, bool SOFTCAP>
-__global__ void __launch_bounds__(192, 2)
+template <int D_, bool BF16, bool SOFTCAP>
+__global__ void __launch_bounds__(192, PersistCfg<D_>::CTAS_PER_SM)
 attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                         const __grid_constant__ CUtensorMap tm_v, const FwdParams p, const SchedParams sp) {
-  using Cfg = PersistCfg;
+  using Cfg = PersistCfg<D_>;
   constexpr int SL = Cfg::SLOTS, D = Cfg::D, BN = Cfg::BN, BM = Cfg::BM, SB = Cfg::SB;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -399,11 +400,11 @@ inline int sched_counter_for_launch(unsigned int** out) {
   return B200_OK;
 }
 
-template <bool BF16, bool SOFTCAP>
+template <int D_, bool BF16, bool SOFTCAP>
 int launch_attn_fwd_persist(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
                             cudaStream_t stream) {
-  using Cfg = PersistCfg;
-  auto kern = attn_fwd_persist_kernel<BF16, SOFTCAP>;
+  using Cfg = PersistCfg<D_>;
+  auto kern = attn_fwd_persist_kernel<D_, BF16, SOFTCAP>;
   static thread_local int configured_dev = -1;
   int dev = 0;
   B200_CUDA_TRY(cudaGetDevice(&dev));
@@ -418,13 +419,13 @@ int launch_attn_fwd_persist(const CUtensorMap& tq, const CUtensorMap& tk, const 
   sp.total_items = p.batch * p.heads * sp.n_q_tiles;
   // group size: K/V of a group within a quarter of L2 (~32 MB), at least 1 and at most 32 units
   {
-    const int64_t kv_bytes_per_unit = (int64_t)2 * p.kv_len * 128 * 2;
+    const int64_t kv_bytes_per_unit = (int64_t)2 * p.kv_len * D_ * 2;
     int gh = (int)std::max<int64_t>(1, std::min<int64_t>(32, ((int64_t)32 << 20) / kv_bytes_per_unit));
     static const char* env = std::getenv("B200_ATTN_GROUP_HEADS");
     if (env != nullptr && std::atoi(env) > 0) gh = std::atoi(env);
     sp.group_heads = gh;
   }
-  const int grid = std::min(sp.total_items, 2 * sm_count());
+  const int grid = std::min(sp.total_items, Cfg::CTAS_PER_SM * sm_count());
   kern<<<grid, 192, Cfg::SMEM_BYTES_P, stream>>>(tq, tk, tv, p, sp);
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
