@@ -37,6 +37,7 @@ SIGNATURES = {
                                    _i, _i, _f, _f, _vp]),
     "b200_attn_score_workspace_bytes": (_i64, [_i, _i, _i, _i]),
     "b200_attn_score": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]),
+    "b200_attn_score_gqa": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]),
     "b200_attn_score_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]),
     "b200_attn_corm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "b200_avg_pool1d_f32": (_i, [_vp, _vp, _i64, _i, _i, _vp]),

@@ -86,14 +86,24 @@ def _attn_score_impl(q, k, v, want_sq, causal, window, softcap, scale):
   dev = _check_qkv(where, q, k, v)
   B, Sq, H, D = q.shape
   Skv, Hk = k.size(1), k.size(2)
-  if H != Hk:
-    raise ValueError(f"{where}: needs heads == kv heads (the reference asserts group_size == 1)")
+  if H != Hk and want_sq:
+    raise ValueError(f"{where}: the squared statistic needs heads == kv heads (the group mean does not commute "
+                     "with the square; the reference asserts group_size == 1)")
   if scale is None or scale <= 0:
     scale = 1.0 / math.sqrt(D)
   out = torch.empty_like(q)
-  score = torch.empty((B, H, Skv), dtype=torch.float32, device=dev)
+  score = torch.empty((B, Hk, Skv), dtype=torch.float32, device=dev)
   score_sq = torch.empty((B, H, Skv), dtype=torch.float32, device=dev) if want_sq else None
   ws, nbytes = _workspace(dev, B, Sq, Skv, H)
+  if H != Hk:
+    # grouped-query attention: mean over the query heads of a K/V head, then the column sum (kernels/roco.py:39-40)
+    with torch.cuda.device(dev):
+      st = _lib.load().b200_attn_score_gqa(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                           score.data_ptr(), ws.data_ptr(), nbytes, B, Sq, Skv, H, Hk, D,
+                                           _dtype_code(q, where), int(bool(causal)), int(window), float(softcap),
+                                           float(scale), _stream_ptr(dev))
+    _lib.check(st, where)
+    return out, score
   with torch.cuda.device(dev):
     st = _lib.load().b200_attn_score(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), score.data_ptr(),
                                      score_sq.data_ptr() if want_sq else None, ws.data_ptr(), nbytes, B, Sq, Skv, H,

@@ -39,6 +39,7 @@ struct SweepParams {
   float* partial_sq;    // same shape, RoCo only
   int batch, heads, q_len, kv_len, delta, causal, window;
   int lse_stride, kv_pad, n_chunks, chunk_blocks;
+  int kv_group;         // query heads per K/V head (the key operand of head h is K head h / kv_group)
   float scale_log2, cap_in, cap_out, inv_tau;
 };
 
@@ -89,7 +90,8 @@ __device__ __forceinline__ void sweep_producer(const SweepCtx<Cfg>& c, const Swe
   mbar_expect_tx(&c.bars[Cfg::BAR_A_FULL], Cfg::A_BYTES);
 #pragma unroll
   for (int ks = 0; ks < 2; ++ks)
-    tma_load_4d(c.sA + ks * (Cfg::BM * 128), tm_a, &c.bars[Cfg::BAR_A_FULL], ks * 64, c.h, c.a0, c.b);
+    tma_load_4d(c.sA + ks * (Cfg::BM * 128), tm_a, &c.bars[Cfg::BAR_A_FULL], ks * 64,
+                Cfg::MODE == SWEEP_KF_ROWLSE ? c.h : c.h / p.kv_group, c.a0, c.b);
   bool ok = true;
   int n_issued = 0;
   for (int blk = c.blk_lo; blk < c.blk_hi; ++blk) {
@@ -101,8 +103,8 @@ __device__ __forceinline__ void sweep_producer(const SweepCtx<Cfg>& c, const Swe
     mbar_expect_tx(&c.bars[Cfg::BAR_X_FULL + st], Cfg::X_STAGE_BYTES);
 #pragma unroll
     for (int ks = 0; ks < 2; ++ks)
-      tma_load_4d(c.sX + st * Cfg::X_STAGE_BYTES + ks * (BX * 128), tm_x, &c.bars[Cfg::BAR_X_FULL + st], ks * 64, c.h,
-                  blk * BX, c.b);
+      tma_load_4d(c.sX + st * Cfg::X_STAGE_BYTES + ks * (BX * 128), tm_x, &c.bars[Cfg::BAR_X_FULL + st], ks * 64,
+                  Cfg::MODE == SWEEP_KF_ROWLSE ? c.h / p.kv_group : c.h, blk * BX, c.b);
     if constexpr (Cfg::N_STAGE_BYTES > 0) {
       if (use > 0 && !mbar_wait(&c.bars[Cfg::BAR_N_EMPTY + st], (use - 1) & 1, c.abort_flag, WAIT_N_EMPTY)) {
         ok = false;
@@ -454,17 +456,20 @@ attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   if (warp == 0) tmem_dealloc(c.tmem_base, Cfg::TMEM_COLS);
 }
 
-// Adds the per-chunk partial vectors in chunk order: out[bh][j] = sum_c partial[bh][c][j].
+// Adds the per-chunk partial vectors in chunk order: out[bh][j] = mul * sum_c partial[bh][c][j].
+// Grouped-query scores: the partial vectors of the g query heads of one K/V head are adjacent, so the same loop
+// over g * n_chunks rows with mul = 1/g yields the group mean of the column sums
+// (kernels/roco.py:39-40 averages the probabilities over the group before summing over the queries).
 __global__ void __launch_bounds__(256)
 score_reduce_kernel(float* __restrict__ out, float* __restrict__ out_sq, const float* __restrict__ partial,
-                    const float* __restrict__ partial_sq, int kv_len, int kv_pad, int n_chunks) {
+                    const float* __restrict__ partial_sq, int kv_len, int kv_pad, int n_chunks, float mul) {
   const int bh = blockIdx.y;
   const int j = blockIdx.x * 256 + threadIdx.x;
   if (j >= kv_len) return;
   const float* src = partial + (int64_t)bh * n_chunks * kv_pad + j;
   float a = 0.f;
   for (int cidx = 0; cidx < n_chunks; ++cidx) a += src[(int64_t)cidx * kv_pad];
-  out[(int64_t)bh * kv_len + j] = a;
+  out[(int64_t)bh * kv_len + j] = mul == 1.0f ? a : a * mul;
   if (out_sq != nullptr) {
     const float* src2 = partial_sq + (int64_t)bh * n_chunks * kv_pad + j;
     float a2 = 0.f;
@@ -577,7 +582,12 @@ avg_pool1d_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t
 inline int attn_score_impl(const void* q, const void* k, const void* v, void* out, float* score, float* score_sq,
                            void* workspace, int64_t workspace_bytes, int batch, int q_len, int kv_len, int heads,
                            int head_dim, int dtype, int causal, int window, float softcap, float scale,
-                           cudaStream_t stream, uint8_t* corm_flags = nullptr) {
+                           cudaStream_t stream, uint8_t* corm_flags = nullptr, int kv_heads = 0) {
+  if (kv_heads <= 0) kv_heads = heads;
+  if (heads % kv_heads != 0) return B200_ERR_BAD_ARGUMENT;
+  const int group = heads / kv_heads;
+  // the group mean commutes with the column sum, but not with the square or the Corm threshold test
+  if (group > 1 && (score_sq != nullptr || corm_flags != nullptr)) return B200_ERR_UNSUPPORTED;
   int rc = score_common_checks(q, k, v, out, workspace, workspace_bytes, batch, q_len, kv_len, heads, head_dim, dtype);
   if (rc != B200_OK) return rc;
   if (!score) return B200_ERR_BAD_ARGUMENT;
@@ -586,13 +596,13 @@ inline int attn_score_impl(const void* q, const void* k, const void* v, void* ou
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   float* lse = reinterpret_cast<float*>(ws + w.lse_off);
 
-  rc = attn_fwd_impl_lse_stride(q, k, v, out, lse, w.lse_stride, batch, q_len, kv_len, heads, heads, head_dim, dtype,
-                                causal, window, softcap, scale, stream);
+  rc = attn_fwd_impl_lse_stride(q, k, v, out, lse, w.lse_stride, batch, q_len, kv_len, heads, kv_heads, head_dim,
+                                dtype, causal, window, softcap, scale, stream);
   if (rc != B200_OK) return rc;
 
   const bool bf16 = dtype == B200_BF16;
   CUtensorMap ta, tx, tn;
-  if ((rc = make_bshd_tensor_map(&ta, k, batch, kv_len, heads, head_dim, 128, bf16)) != B200_OK) return rc;
+  if ((rc = make_bshd_tensor_map(&ta, k, batch, kv_len, kv_heads, head_dim, 128, bf16)) != B200_OK) return rc;
   if ((rc = make_bshd_tensor_map(&tx, q, batch, q_len, heads, head_dim, 128, bf16)) != B200_OK) return rc;
   tn = ta;  // unused
 
@@ -612,6 +622,7 @@ inline int attn_score_impl(const void* q, const void* k, const void* v, void* ou
   p.kv_pad = w.kv_pad;
   p.n_chunks = w.n_chunks_colsum;
   p.chunk_blocks = kSweepChunkBlocks;
+  p.kv_group = group;
   const float kLog2e = 1.4426950408889634f;
   p.scale_log2 = scale * kLog2e;
   p.cap_in = softcap > 0.f ? scale / softcap : 0.f;
@@ -633,9 +644,9 @@ inline int attn_score_impl(const void* q, const void* k, const void* v, void* ou
 #undef B200_SWEEP0
   if (rc != B200_OK) return rc;
 
-  dim3 rgrid((kv_len + 255) / 256, batch * heads);
+  dim3 rgrid((kv_len + 255) / 256, batch * kv_heads);
   score_reduce_kernel<<<rgrid, 256, 0, stream>>>(score, score_sq, p.partial, p.partial_sq, kv_len, w.kv_pad,
-                                                 p.n_chunks);
+                                                 p.n_chunks * group, 1.0f / (float)group);
   B200_CUDA_TRY(cudaGetLastError());
   if (corm_flags != nullptr) {
     corm_reduce_kernel<<<rgrid, 256, 0, stream>>>(corm_flags, p.partial_sq, kv_len, w.kv_pad, p.n_chunks);
@@ -690,6 +701,7 @@ inline int attn_kf_impl(const void* q, const void* k, const void* v, const float
   p.chunk_blocks = kSweepChunkBlocks;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.inv_tau = 1.0f / tau;
+  p.kv_group = 1;
 
   // sweep 1: Lz_i = log2 sum_j exp2(z_ij), one CTA per 128 queries
   const int q_tiles = (q_len + 127) / 128;
@@ -703,7 +715,8 @@ inline int attn_kf_impl(const void* q, const void* k, const void* v, const float
   if (rc != B200_OK) return rc;
 
   dim3 rgrid((kv_len + 255) / 256, batch * heads);
-  score_reduce_kernel<<<rgrid, 256, 0, stream>>>(kf_score, nullptr, p.partial, nullptr, kv_len, w.kv_pad, p.n_chunks);
+  score_reduce_kernel<<<rgrid, 256, 0, stream>>>(kf_score, nullptr, p.partial, nullptr, kv_len, w.kv_pad, p.n_chunks,
+                                                 1.0f);
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
 }

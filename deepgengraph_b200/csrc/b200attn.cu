@@ -298,6 +298,14 @@ int b200_kv_evict_topk(const float* score, const void* k, const void* v, void* k
                             (cudaStream_t)stream);
 }
 
+int b200_attn_score_gqa(const void* q, const void* k, const void* v, void* out, float* score, void* workspace,
+                        int64_t workspace_bytes, int batch, int q_len, int kv_len, int heads, int kv_heads,
+                        int head_dim, int dtype, int causal, int window, float softcap, float scale, void* stream) {
+  if (kv_heads <= 0) return B200_ERR_BAD_ARGUMENT;
+  return attn_score_impl(q, k, v, out, score, nullptr, workspace, workspace_bytes, batch, q_len, kv_len, heads,
+                         head_dim, dtype, causal, window, softcap, scale, (cudaStream_t)stream, nullptr, kv_heads);
+}
+
 int b200_kv_evict_roco(const float* score, const float* score_sq, const void* k, const void* v, void* kv_cache,
                        int32_t* indices, int batch, int seq_len, int heads, int head_dim, int q_len, int budget,
                        int recent, int dtype, void* stream) {

@@ -153,6 +153,21 @@ int b200_attn_score(const void* q, const void* k, const void* v, void* out, floa
                     int window, float softcap, float scale, void* stream);
 
 /*
+ * b200_attn_score for grouped-query attention (heads > kv_heads): the probabilities are averaged over the
+ * heads / kv_heads query heads that share a K/V head before they are summed over the queries
+ *   -- the group_size > 1 branch of kernels/roco.py:39-40 and figure/membound/attn.py:84-88 (the reference's
+ *      modules assert group_size == 1, so that branch never runs there).
+ * k, v   [batch, kv_len, kv_heads, head_dim];  score float32 [batch, kv_heads, kv_len].
+ * The workspace is sized for `heads` (b200_attn_score_workspace_bytes(batch, q_len, kv_len, heads)).
+ * Only the plain column sums are offered: the mean over the group does not commute with the square
+ * (RoCo's second statistic), which returns B200_ERR_UNSUPPORTED for heads != kv_heads.
+ */
+int b200_attn_score_gqa(const void* q, const void* k, const void* v, void* out, float* score,
+                        void* workspace, int64_t workspace_bytes, int batch, int q_len, int kv_len,
+                        int heads, int kv_heads, int head_dim, int dtype, int causal, int window,
+                        float softcap, float scale, void* stream);
+
+/*
  * b200_attn_score without a caller-provided workspace and without any device allocation.
  * (No counterpart in the reference project: its generated launchers allocate freely through PyTorch.)
  *

@@ -129,3 +129,22 @@ def test_config4_slice_full_length(cuda_device):
   out, s = att.attn_kf_fwd(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), exp_rand.to(cuda_device), tau=1.0)
   torch.testing.assert_close(out.float().cpu(), ref["out"], **TOL)
   torch.testing.assert_close(s.cpu(), ref["kf"], **STOL)
+
+
+@pytest.mark.parametrize("shape", [(1, 512, 512, 4, 2), (2, 384, 640, 6, 2), (1, 1024, 1024, 8, 1)])
+def test_grouped_query_scores_are_the_group_mean(cuda_device, shape):
+  # heads > kv heads: probabilities averaged over the query heads of a K/V head, then summed over the queries
+  # (the group_size > 1 branch of kernels/roco.py:39-40, never run by the reference's own modules)
+  B, Sq, Skv, H, Hk = shape
+  q = _randn((B, Sq, H, 128), torch.bfloat16, 41)
+  k = _randn((B, Skv, Hk, 128), torch.bfloat16, 42)
+  v = _randn((B, Skv, Hk, 128), torch.bfloat16, 43)
+  ref = rm.attention_ref(q, k, v, causal=True, want=("out", "colsum"))
+  want = ref["colsum"].view(B, Hk, H // Hk, Skv).mean(dim=2)
+  out, score = att.attn_score_fwd(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device))
+  assert score.shape == (B, Hk, Skv)
+  torch.testing.assert_close(out.float().cpu(), ref["out"], rtol=2e-2, atol=2e-2)
+  torch.testing.assert_close(score.cpu(), want, **STOL)
+  torch.testing.assert_close(score.sum(dim=-1).cpu(), torch.full((B, Hk), float(Sq)), rtol=1e-3, atol=1e-3)
+  with pytest.raises(ValueError):
+    att.attn_score_fwd(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), want_sq=True)
