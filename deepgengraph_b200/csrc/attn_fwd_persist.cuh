@@ -60,7 +60,8 @@ struct PersistCfg : FwdCfg<D_, 64, 1, 2> {
   using Base = FwdCfg<D_, 64, 1, 2>;
   static constexpr int BAR_SCHED = Base::NUM_BARS;        // [2] tile descriptor slot k % 2 published
   static constexpr int BAR_Q_FREE = BAR_SCHED + 2;        // last S MMA of a tile retired: Q buffer reusable
-  static constexpr int NUM_BARS_P = BAR_Q_FREE + 1;
+  static constexpr int BAR_SCHED_FREE = BAR_Q_FREE + 1;   // [2] descriptor slot read by all five consumers
+  static constexpr int NUM_BARS_P = BAR_SCHED_FREE + 2;
   static constexpr int SMEM_BYTES_P = Base::SMEM_TILES + NUM_BARS_P * 8 + 64 + 1024;
   static_assert(SMEM_BYTES_P <= Base::SMEM_BUDGET, "shared memory budget exceeded");
 };
@@ -95,7 +96,8 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 #pragma unroll
     for (int i = 0; i < Cfg::NUM_BARS_P; ++i) {
       const bool is_p_full = (i >= Cfg::BAR_P_FULL && i < Cfg::BAR_P_FULL + SB);   // 4 softmax warps
-      mbar_init(&c.bars[i], is_p_full ? 4u : 1u);
+      const bool is_sched_free = (i >= Cfg::BAR_SCHED_FREE && i < Cfg::BAR_SCHED_FREE + 2);   // + the MMA issuer
+      mbar_init(&c.bars[i], is_sched_free ? 5u : is_p_full ? 4u : 1u);
     }
     *c.abort_flag = 0;
     fence_mbar_init();
@@ -125,6 +127,8 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     for (int k = 0;; ++k) {
       if (!mbar_wait(&c.bars[Cfg::BAR_SCHED + (k & 1)], (k >> 1) & 1, c.abort_flag, WAIT_SCHED)) break;
       const int item = sched[k & 1];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&c.bars[Cfg::BAR_SCHED_FREE + (k & 1)]);   // slot may be rewritten for tile k + 2
       if (item < 0) break;
       const TileInfo t = decode_item(item, p, sp, BN);
       const int row = t.q0 + warp_q * 32 + lane;
@@ -188,8 +192,13 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       for (int k = 0; ok; ++k) {
         const int item = (int)atomicAdd(&sp.counter[0], 1u);
         const bool valid = item < sp.total_items;
-        // Slot k % 2 was last read for tile k-2; both consumers are past it: this thread has already waited for
-        // Q_FREE(k-1), which the issuer commits only after the softmax warpgroup delivered P for tile k-1.
+        // Slot k % 2 still holds the descriptor of tile k-2 until the four softmax warps and the issuer have all
+        // read it (with tiles of one or two key blocks the issuer can finish a tile's S MMAs, and this thread
+        // its loads, before the softmax warpgroup has even left the previous tile's epilogue).
+        if (k >= 2 && !mbar_wait(&c.bars[Cfg::BAR_SCHED_FREE + (k & 1)], ((k >> 1) - 1) & 1, c.abort_flag, WAIT_SCHED)) {
+          ok = false;
+          break;
+        }
         sched[k & 1] = valid ? item : -1;
         mbar_arrive(&c.bars[Cfg::BAR_SCHED + (k & 1)]);
         if (!valid) {
@@ -284,6 +293,8 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     for (int k = 0; ok; ++k) {
       if (!mbar_wait(&c.bars[Cfg::BAR_SCHED + (k & 1)], (k >> 1) & 1, c.abort_flag, WAIT_SCHED)) break;
       const int item = sched[k & 1];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&c.bars[Cfg::BAR_SCHED_FREE + (k & 1)]);
       if (item < 0) break;
       const TileInfo t = decode_item(item, p, sp, BN);
       const int nb = t.hi - t.lo;

@@ -202,6 +202,25 @@ def test_views_with_unaligned_strides_are_rejected(cuda_device):
     att.attn_fwd(q, k, v)
 
 
+@pytest.mark.parametrize("case", ["short_sequences", "narrow_window", "head_dim_256"])
+def test_many_tiny_tiles_per_cta(cuda_device, case):
+  # tiles of one or two key blocks, several per persistent CTA: the MMA issuer and the loader can run a whole
+  # tile ahead of the softmax warpgroup, so the tile hand-over itself is what is exercised here
+  if case == "short_sequences":
+    B, S, H, D, window = 8, 128, 64, 128, 0            # 512 tiles of 2 key blocks
+  elif case == "narrow_window":
+    B, S, H, D, window = 2, 2048, 16, 128, 32          # 512 tiles of <= 2 key blocks
+  else:
+    B, S, H, D, window = 4, 256, 48, 256, 0            # 384 tiles on a one-CTA-per-SM grid
+  q, k, v = _qkv(B, S, S, H, H, D, torch.bfloat16, seed=51)
+  ref = rm.attention_ref(q, k, v, causal=True, window=window, head_chunk=16)["out"]
+  qd, kd, vd = q.to(cuda_device), k.to(cuda_device), v.to(cuda_device)
+  out = att.attn_fwd(qd, kd, vd, causal=True, window=window)
+  torch.testing.assert_close(out.float().cpu(), ref, **TOL)
+  for _ in range(3):
+    assert torch.equal(att.attn_fwd(qd, kd, vd, causal=True, window=window), out)
+
+
 def test_host_validation(cuda_device):
   q, k, v = (t.to(cuda_device) for t in _qkv(1, 128, 128, 2, 2, 128, torch.bfloat16))
   with pytest.raises(TypeError):
