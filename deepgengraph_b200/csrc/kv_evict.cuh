@@ -6,7 +6,7 @@
 //     k_cache = gather(k, idx); v_cache = gather(v, idx); kv_cache = cat([k_cache, v_cache], dim=1)
 // i.e. the result only depends on the SET of the top-`budget` keys; it is emitted in ascending key order.
 //
-// One CTA per (batch, head): a 4-pass radix select (8 bits per pass, shared-memory histogram) finds the value of
+// One to eight CTAs per (batch, head): a 4-pass radix select (8 bits per pass, shared-memory histogram) finds the value of
 // the budget-th largest score, one ordered compaction pass emits the selected key indices already sorted, and the
 // CTA then copies the selected rows with 16-byte accesses.  Ties at the threshold value are resolved towards the
 // lower key index (torch.topk leaves that choice unspecified).  HBM-bound: reads the scores five times from L2
@@ -48,56 +48,138 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums, int* 
   return base + incl - v;
 }
 
+
+// Block-wide radix select (4 passes of 8 bits, most significant first): key value of the `want`-th largest key
+// among the keys with use(i) true.  Returns the threshold; *need_equal = how many keys EQUAL to it belong to
+// the top `want`.  The histogram update is aggregated per warp (real score vectors put most keys into a few
+// exponent bins, which would serialise plain shared-memory atomics), and the bin that holds the want-th key is
+// found with one block-wide suffix scan instead of a serial walk over the 256 bins.
+template <class KeyFn, class UseFn>
+__device__ __forceinline__ uint32_t block_radix_select(KeyFn key, UseFn use, int seq, int want, int* hist,
+                                                       int* warp_sums, uint32_t* s_prefix, int* s_remaining,
+                                                       int* need_equal) {
+  static_assert(kEvictThreads == 256, "one thread per histogram bin");
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    *s_prefix = 0;
+    *s_remaining = want;
+  }
+  uint32_t mask = 0;
+  const int lane = threadIdx.x & 31;
+  for (int pass = 3; pass >= 0; --pass) {
+    hist[threadIdx.x] = 0;
+    __syncthreads();
+    const uint32_t prefix = *s_prefix;
+    const int remaining = *s_remaining;
+    const int shift = pass * 8;
+    for (int i0 = 0; i0 < seq; i0 += kEvictThreads) {
+      const int i = i0 + threadIdx.x;
+      uint32_t bin = 0xffffffffu;   // not counted
+      if (i < seq && use(i)) {
+        const uint32_t u = key(i);
+        if ((u & mask) == prefix) bin = (u >> shift) & 0xff;
+      }
+      const uint32_t peers = __match_any_sync(0xffffffffu, bin);
+      if (bin != 0xffffffffu && lane == __ffs(peers) - 1) atomicAdd(&hist[bin], __popc(peers));
+    }
+    __syncthreads();
+    // thread t owns bin 255 - t: `above` = keys in higher bins; the wanted bin has above < remaining <= above + own
+    const int own = hist[255 - threadIdx.x];
+    int total;
+    const int above = block_exclusive_scan(own, warp_sums, &total);
+    if (above < remaining && remaining <= above + own) {
+      *s_prefix = prefix | ((uint32_t)(255 - threadIdx.x) << shift);
+      *s_remaining = remaining - above;
+    } else if (threadIdx.x == 255 && remaining > total) {   // fewer candidates than wanted: take them all
+      *s_prefix = prefix;
+      *s_remaining = remaining - (total - own);
+    }
+    mask |= 0xffu << shift;
+    __syncthreads();
+  }
+  *need_equal = *s_remaining;
+  return *s_prefix;
+}
+
+
+// Gather of the selected rows: kv_cache[b, 0, i, h, :] = k[b, idx_i, h, :], kv_cache[b, 1, i, h, :] = v[b, idx_i, h, :].
+// The CTAs of one (batch, head) -- gridDim.y of them, each of which has made the same selection -- take
+// interleaved slices of the rows; four 16-byte K and V loads are in flight per thread before the first store.
+__device__ __forceinline__ void gather_selected_rows(const int32_t* s_idx, const uint8_t* __restrict__ k,
+                                                     const uint8_t* __restrict__ v, uint8_t* __restrict__ kv_cache,
+                                                     int b, int h, int seq, int heads, int row_bytes, int keep) {
+  const int vec_per_row = row_bytes / 16;                 // row_bytes is a multiple of 16, checked on the host
+  const int64_t src_row_stride = (int64_t)heads * row_bytes;                 // [B, S, H, D]
+  const int64_t src_batch = (int64_t)b * seq * src_row_stride + (int64_t)h * row_bytes;
+  const int64_t dst_plane = (int64_t)keep * heads * row_bytes;               // [B, 2, keep, H, D]
+  const int64_t dst_batch = (int64_t)b * 2 * dst_plane + (int64_t)h * row_bytes;
+  const int total = keep * vec_per_row;
+  const int stride = kEvictThreads * gridDim.y;
+  constexpr int U = 4;
+  for (int g0 = blockIdx.y * kEvictThreads + threadIdx.x; g0 < total; g0 += U * stride) {
+    uint4 kk[U], vv[U];
+    int64_t dst[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int g = g0 + u * stride;
+      if (g < total) {
+        const int r = g / vec_per_row, c = g - r * vec_per_row;
+        const int64_t src = src_batch + (int64_t)s_idx[r] * src_row_stride + c * 16;
+        dst[u] = dst_batch + (int64_t)r * src_row_stride + c * 16;
+        kk[u] = *reinterpret_cast<const uint4*>(k + src);
+        vv[u] = *reinterpret_cast<const uint4*>(v + src);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (g0 + u * stride < total) {
+        *reinterpret_cast<uint4*>(kv_cache + dst[u]) = kk[u];
+        *reinterpret_cast<uint4*>(kv_cache + dst[u] + dst_plane) = vv[u];
+      }
+    }
+  }
+}
+
+// CTAs per (batch, head): enough to fill the GPU when there are few heads (every CTA repeats the selection,
+// which reads 16 KB of scores from L2, and gathers its share of the rows)
+inline int evict_ctas_per_head(int batch_heads) {
+  const int want = (2 * sm_count() + batch_heads - 1) / batch_heads;
+  return std::max(1, std::min(8, want));
+}
+
 template <int ELEM_BYTES>
 __global__ void __launch_bounds__(kEvictThreads)
 kv_evict_topk_kernel(const float* __restrict__ score, const uint8_t* __restrict__ k, const uint8_t* __restrict__ v,
                      uint8_t* __restrict__ kv_cache, int32_t* __restrict__ indices_out, int seq, int heads,
-                     int head_dim, int budget) {
+                     int head_dim, int budget, int staged) {
   __shared__ int hist[256];
   __shared__ int warp_sums[kEvictThreads / 32];
   __shared__ uint32_t s_prefix;
   __shared__ int s_remaining;
   extern __shared__ int32_t s_idx[];   // [budget] selected key indices, ascending
+  uint32_t* s_keys = reinterpret_cast<uint32_t*>(s_idx + budget);   // [seq] order keys, when they fit (`staged`)
 
   const int bh = blockIdx.x, b = bh / heads, h = bh - b * heads;
   const float* sc = score + (int64_t)bh * seq;
 
+  // The five passes below each touch every score; staged in shared memory once (all loads in flight together)
+  // they cost a shared-memory read instead of a dependent L2 round trip per pass.
+  if (staged) {
+#pragma unroll 8
+    for (int i = threadIdx.x; i < seq; i += kEvictThreads) s_keys[i] = score_key(sc[i]);
+  }
+  auto key_of = [&](int i) { return staged ? s_keys[i] : score_key(sc[i]); };
+
   // ---- radix select: key value of the budget-th largest score ----
-  if (threadIdx.x == 0) {
-    s_prefix = 0;
-    s_remaining = budget;
-  }
-  uint32_t mask = 0;
-  for (int pass = 3; pass >= 0; --pass) {
-    for (int i = threadIdx.x; i < 256; i += kEvictThreads) hist[i] = 0;
-    __syncthreads();
-    const uint32_t prefix = s_prefix;
-    const int shift = pass * 8;
-    for (int i = threadIdx.x; i < seq; i += kEvictThreads) {
-      const uint32_t u = score_key(sc[i]);
-      if ((u & mask) == prefix) atomicAdd(&hist[(u >> shift) & 0xff], 1);
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      int remaining = s_remaining, bin = 255;
-      for (; bin > 0; --bin) {
-        if (hist[bin] >= remaining) break;
-        remaining -= hist[bin];
-      }
-      s_prefix = prefix | ((uint32_t)bin << shift);
-      s_remaining = remaining;   // how many keys equal to the final prefix are still needed
-    }
-    mask |= 0xffu << shift;
-    __syncthreads();
-  }
-  const uint32_t thr = s_prefix;
-  const int need_equal = s_remaining;
+  int need_equal;
+  const uint32_t thr = block_radix_select(key_of, [](int) { return true; }, seq, budget, hist, warp_sums, &s_prefix,
+                                          &s_remaining, &need_equal);
 
   // ---- ordered compaction: selected indices in ascending order ----
   int sel_base = 0, eq_base = 0;
   for (int i0 = 0; i0 < seq; i0 += kEvictThreads) {
     const int i = i0 + threadIdx.x;
-    const uint32_t u = i < seq ? score_key(sc[i]) : 0u;
+    const uint32_t u = i < seq ? key_of(i) : 0u;
     const int is_eq = (i < seq && u == thr) ? 1 : 0;
     int eq_total, sel_total;
     const int eq_before = eq_base + block_exclusive_scan(is_eq, warp_sums, &eq_total);
@@ -109,24 +191,10 @@ kv_evict_topk_kernel(const float* __restrict__ score, const uint8_t* __restrict_
   }
   __syncthreads();
 
-  if (indices_out != nullptr)
+  if (indices_out != nullptr && blockIdx.y == 0)
     for (int i = threadIdx.x; i < budget; i += kEvictThreads) indices_out[(int64_t)bh * budget + i] = s_idx[i];
 
-  // ---- gather: kv_cache[b, 0, i, h, :] = k[b, idx_i, h, :], kv_cache[b, 1, i, h, :] = v[b, idx_i, h, :] ----
-  const int row_bytes = head_dim * ELEM_BYTES;            // multiple of 16, checked on the host
-  const int vec_per_row = row_bytes / 16;
-  const int64_t src_row_stride = (int64_t)heads * row_bytes;                 // [B, S, H, D]
-  const int64_t src_batch = (int64_t)b * seq * src_row_stride + (int64_t)h * row_bytes;
-  const int64_t dst_plane = (int64_t)budget * heads * row_bytes;             // [B, 2, budget, H, D]
-  const int64_t dst_batch = (int64_t)b * 2 * dst_plane + (int64_t)h * row_bytes;
-  const int total = budget * vec_per_row;
-  for (int g = threadIdx.x; g < total; g += kEvictThreads) {
-    const int r = g / vec_per_row, c = g - r * vec_per_row;
-    const int64_t src = src_batch + (int64_t)s_idx[r] * src_row_stride + c * 16;
-    const int64_t dst = dst_batch + (int64_t)r * src_row_stride + c * 16;
-    *reinterpret_cast<uint4*>(kv_cache + dst) = *reinterpret_cast<const uint4*>(k + src);
-    *reinterpret_cast<uint4*>(kv_cache + dst + dst_plane) = *reinterpret_cast<const uint4*>(v + src);
-  }
+  gather_selected_rows(s_idx, k, v, kv_cache, b, h, seq, heads, head_dim * ELEM_BYTES, budget);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -150,50 +218,12 @@ __device__ __forceinline__ float roco_std(float score, float sq, float q_len) {
   return __fsqrt_rn(__fsub_rn(__fdiv_rn(sq, q_len), __fmul_rn(m, m)));
 }
 
-// Block-wide radix select: key value of the `want`-th largest key among the keys with use(i) true.
-// Returns the threshold; *need_equal = how many keys EQUAL to it belong to the top `want`.
-template <class KeyFn, class UseFn>
-__device__ __forceinline__ uint32_t block_radix_select(KeyFn key, UseFn use, int seq, int want, int* hist,
-                                                       uint32_t* s_prefix, int* s_remaining, int* need_equal) {
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    *s_prefix = 0;
-    *s_remaining = want;
-  }
-  uint32_t mask = 0;
-  for (int pass = 3; pass >= 0; --pass) {
-    for (int i = threadIdx.x; i < 256; i += kEvictThreads) hist[i] = 0;
-    __syncthreads();
-    const uint32_t prefix = *s_prefix;
-    const int shift = pass * 8;
-    for (int i = threadIdx.x; i < seq; i += kEvictThreads) {
-      if (!use(i)) continue;
-      const uint32_t u = key(i);
-      if ((u & mask) == prefix) atomicAdd(&hist[(u >> shift) & 0xff], 1);
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      int remaining = *s_remaining, bin = 255;
-      for (; bin > 0; --bin) {
-        if (hist[bin] >= remaining) break;
-        remaining -= hist[bin];
-      }
-      *s_prefix = prefix | ((uint32_t)bin << shift);
-      *s_remaining = remaining;
-    }
-    mask |= 0xffu << shift;
-    __syncthreads();
-  }
-  *need_equal = *s_remaining;
-  return *s_prefix;
-}
-
 template <int ELEM_BYTES>
 __global__ void __launch_bounds__(kEvictThreads)
 kv_evict_roco_kernel(const float* __restrict__ score, const float* __restrict__ score_sq,
                      const uint8_t* __restrict__ k, const uint8_t* __restrict__ v, uint8_t* __restrict__ kv_cache,
                      int32_t* __restrict__ indices_out, int seq, int heads, int head_dim, float q_len, int budget,
-                     int recent) {
+                     int recent, int staged) {
   __shared__ int hist[256];
   __shared__ int warp_sums[kEvictThreads / 32];
   __shared__ uint32_t s_prefix;
@@ -201,20 +231,30 @@ kv_evict_roco_kernel(const float* __restrict__ score, const float* __restrict__ 
   extern __shared__ int32_t s_dyn[];
   const int keep = budget + recent;
   int32_t* s_idx = s_dyn;                                        // [keep] selected key indices, ascending
-  uint8_t* in_a = reinterpret_cast<uint8_t*>(s_dyn + keep);      // [seq] 1 = key belongs to A
+  uint32_t* s_std = reinterpret_cast<uint32_t*>(s_dyn + keep);   // [seq] order keys of std   (when `staged`)
+  uint32_t* s_mean = s_std + (staged ? seq : 0);                 // [seq] order keys of score / q_len
+  uint8_t* in_a = reinterpret_cast<uint8_t*>(s_mean + (staged ? seq : 0));   // [seq] 1 = key belongs to A
 
   const int bh = blockIdx.x, b = bh / heads, h = bh - b * heads;
   const float* sc = score + (int64_t)bh * seq;
   const float* sq = score_sq + (int64_t)bh * seq;
-  auto std_key = [&](int i) { return score_key_nan_high(roco_std(sc[i], sq[i], q_len)); };
-  auto mean_key = [&](int i) { return score_key_nan_high(roco_mean(sc[i], q_len)); };
+  if (staged) {
+#pragma unroll 4
+    for (int i = threadIdx.x; i < seq; i += kEvictThreads) {
+      const float a = sc[i], a2 = sq[i];
+      s_std[i] = score_key_nan_high(roco_std(a, a2, q_len));
+      s_mean[i] = score_key_nan_high(roco_mean(a, q_len));
+    }
+  }
+  auto std_key = [&](int i) { return staged ? s_std[i] : score_key_nan_high(roco_std(sc[i], sq[i], q_len)); };
+  auto mean_key = [&](int i) { return staged ? s_mean[i] : score_key_nan_high(roco_mean(sc[i], q_len)); };
 
   // ---- A: the `recent` keys with the largest std (ties towards the lower index) ----
   for (int i = threadIdx.x; i < seq; i += kEvictThreads) in_a[i] = 0;
   if (recent > 0) {
     int need_eq;
-    const uint32_t thr = block_radix_select(std_key, [](int) { return true; }, seq, recent, hist, &s_prefix,
-                                            &s_remaining, &need_eq);
+    const uint32_t thr = block_radix_select(std_key, [](int) { return true; }, seq, recent, hist, warp_sums,
+                                            &s_prefix, &s_remaining, &need_eq);
     int eq_base = 0;
     for (int i0 = 0; i0 < seq; i0 += kEvictThreads) {
       const int i = i0 + threadIdx.x;
@@ -232,8 +272,8 @@ kv_evict_roco_kernel(const float* __restrict__ score, const float* __restrict__ 
   int need_eq_b = 0;
   uint32_t thr_b = 0xffffffffu;
   if (budget > 0)
-    thr_b = block_radix_select(mean_key, [&](int i) { return in_a[i] == 0; }, seq, budget, hist, &s_prefix,
-                               &s_remaining, &need_eq_b);
+    thr_b = block_radix_select(mean_key, [&](int i) { return in_a[i] == 0; }, seq, budget, hist, warp_sums,
+                               &s_prefix, &s_remaining, &need_eq_b);
 
   // ---- ordered compaction of A u B ----
   int sel_base = 0, eq_base = 0;
@@ -253,24 +293,10 @@ kv_evict_roco_kernel(const float* __restrict__ score, const float* __restrict__ 
   }
   __syncthreads();
 
-  if (indices_out != nullptr)
+  if (indices_out != nullptr && blockIdx.y == 0)
     for (int i = threadIdx.x; i < keep; i += kEvictThreads) indices_out[(int64_t)bh * keep + i] = s_idx[i];
 
-  // ---- gather (layout as kv_evict_topk_kernel) ----
-  const int row_bytes = head_dim * ELEM_BYTES;
-  const int vec_per_row = row_bytes / 16;
-  const int64_t src_row_stride = (int64_t)heads * row_bytes;
-  const int64_t src_batch = (int64_t)b * seq * src_row_stride + (int64_t)h * row_bytes;
-  const int64_t dst_plane = (int64_t)keep * heads * row_bytes;
-  const int64_t dst_batch = (int64_t)b * 2 * dst_plane + (int64_t)h * row_bytes;
-  const int total = keep * vec_per_row;
-  for (int g = threadIdx.x; g < total; g += kEvictThreads) {
-    const int r = g / vec_per_row, c = g - r * vec_per_row;
-    const int64_t src = src_batch + (int64_t)s_idx[r] * src_row_stride + c * 16;
-    const int64_t dst = dst_batch + (int64_t)r * src_row_stride + c * 16;
-    *reinterpret_cast<uint4*>(kv_cache + dst) = *reinterpret_cast<const uint4*>(k + src);
-    *reinterpret_cast<uint4*>(kv_cache + dst + dst_plane) = *reinterpret_cast<const uint4*>(v + src);
-  }
+  gather_selected_rows(s_idx, k, v, kv_cache, b, h, seq, heads, head_dim * ELEM_BYTES, keep);
 }
 
 inline int kv_evict_roco_impl(const float* score, const float* score_sq, const void* k, const void* v,
@@ -282,9 +308,11 @@ inline int kv_evict_roco_impl(const float* score, const float* score_sq, const v
   if (elem_bytes != 2 && elem_bytes != 4) return B200_ERR_BAD_DTYPE;
   if ((head_dim * elem_bytes) % 16 != 0 || !aligned16(k) || !aligned16(v) || !aligned16(kv_cache))
     return B200_ERR_MISALIGNED;
-  const size_t smem = (size_t)(budget + recent) * sizeof(int32_t) + (size_t)((seq + 15) / 16) * 16;
-  if (smem > 200 * 1024) return B200_ERR_UNSUPPORTED;
-  const int grid = batch * heads;
+  const size_t smem_min = (size_t)(budget + recent) * sizeof(int32_t) + (size_t)((seq + 15) / 16) * 16;
+  if (smem_min > 200 * 1024) return B200_ERR_UNSUPPORTED;
+  const int staged = smem_min + (size_t)seq * 8 <= 200 * 1024 ? 1 : 0;
+  const size_t smem = smem_min + (staged ? (size_t)seq * 8 : 0);
+  const dim3 grid(batch * heads, evict_ctas_per_head(batch * heads));
   auto launch = [&](auto kern) -> int {
     static thread_local int configured_dev = -1;
     int dev = 0;
@@ -295,7 +323,7 @@ inline int kv_evict_roco_impl(const float* score, const float* score_sq, const v
     }
     kern<<<grid, kEvictThreads, smem, stream>>>(score, score_sq, (const uint8_t*)k, (const uint8_t*)v,
                                                 (uint8_t*)kv_cache, indices, seq, heads, head_dim, (float)q_len,
-                                                budget, recent);
+                                                budget, recent, staged);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
   };
@@ -312,18 +340,24 @@ inline int kv_evict_topk_impl(const float* score, const void* k, const void* v, 
   if ((head_dim * elem_bytes) % 16 != 0 || !aligned16(k) || !aligned16(v) || !aligned16(kv_cache))
     return B200_ERR_MISALIGNED;
   if (budget > 12288) return B200_ERR_UNSUPPORTED;   // index list lives in shared memory (48 KB)
-  const size_t smem = (size_t)budget * sizeof(int32_t);
-  const int grid = batch * heads;
-  if (elem_bytes == 2)
-    kv_evict_topk_kernel<2><<<grid, kEvictThreads, smem, stream>>>(score, (const uint8_t*)k, (const uint8_t*)v,
-                                                                   (uint8_t*)kv_cache, indices, seq, heads, head_dim,
-                                                                   budget);
-  else
-    kv_evict_topk_kernel<4><<<grid, kEvictThreads, smem, stream>>>(score, (const uint8_t*)k, (const uint8_t*)v,
-                                                                   (uint8_t*)kv_cache, indices, seq, heads, head_dim,
-                                                                   budget);
-  B200_CUDA_TRY(cudaGetLastError());
-  return B200_OK;
+  const size_t smem_idx = (size_t)budget * sizeof(int32_t);
+  const int staged = smem_idx + (size_t)seq * 4 <= 200 * 1024 ? 1 : 0;
+  const size_t smem = smem_idx + (staged ? (size_t)seq * 4 : 0);
+  const dim3 grid(batch * heads, evict_ctas_per_head(batch * heads));
+  auto launch = [&](auto kern) -> int {
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    B200_CUDA_TRY(cudaGetDevice(&dev));
+    if (smem > 48 * 1024 && configured_dev != dev) {
+      B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      configured_dev = dev;
+    }
+    kern<<<grid, kEvictThreads, smem, stream>>>(score, (const uint8_t*)k, (const uint8_t*)v, (uint8_t*)kv_cache, indices,
+                                                seq, heads, head_dim, budget, staged);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+  };
+  return elem_bytes == 2 ? launch(kv_evict_topk_kernel<2>) : launch(kv_evict_topk_kernel<4>);
 }
 
 }  // namespace b200

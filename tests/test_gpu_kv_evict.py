@@ -81,3 +81,22 @@ def test_roco_end_to_end_with_the_fused_scores(cuda_device):
   assert torch.equal(idx.cpu().long(), ref_idx) and torch.equal(cache.cpu(), ref_cache)
   with pytest.raises(RuntimeError):
     att.kv_evict_roco(score, score_sq, k, v, 1024, 1000, 100)      # keeps more keys than there are
+
+
+def test_vectors_too_long_for_shared_memory_staging(cuda_device):
+  # above ~50k keys (top-k) / ~22k keys (RoCo) the order keys no longer fit in shared memory beside the index
+  # list and every pass re-reads the scores instead
+  g = torch.Generator().manual_seed(77)
+  B, S, H, D = 1, 52000, 1, 64
+  score = torch.rand(B, H, S, generator=g) * 10 - 2
+  k = torch.randn(B, S, H, D, generator=g).to(torch.bfloat16)
+  ref_cache, ref_idx = rm.kv_evict_topk_ref(score, k, k, 100)
+  cache, idx = att.kv_evict_topk(score.to(cuda_device), k.to(cuda_device), k.to(cuda_device), 100, return_indices=True)
+  assert torch.equal(idx.cpu().long(), ref_idx) and torch.equal(cache.cpu(), ref_cache)
+  S, Sq = 30000, 64
+  score, score_sq = _roco_stats(B, H, Sq, S, seed=78)
+  k = torch.randn(B, S, H, D, generator=g).to(torch.bfloat16)
+  ref_cache, ref_idx = rm.kv_evict_roco_ref(score, score_sq, k, k, Sq, 200, 20)
+  cache, idx = att.kv_evict_roco(score.to(cuda_device), score_sq.to(cuda_device), k.to(cuda_device), k.to(cuda_device),
+                                 Sq, 200, 20, return_indices=True)
+  assert torch.equal(idx.cpu().long(), ref_idx) and torch.equal(cache.cpu(), ref_cache)
