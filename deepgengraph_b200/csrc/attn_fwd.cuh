@@ -520,6 +520,7 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<Cfg, BF16>& c, const Fw
   if ((threadIdx.x & 127) == 0) B200_TL((3 * 64 + 62) * 8 + 3);   // last P V complete
   const float inv_l = 1.0f / l;
   const bool in_range = row < p.q_len;
+  const bool wide_stores = (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
   uint4* out_row = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) +
                                             (((int64_t)c.b * p.q_len + row) * p.heads + c.h) * (int64_t)D);
 #pragma unroll
@@ -528,14 +529,20 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<Cfg, BF16>& c, const Fw
     tmem_ld32(o_addr + ch * 32, o);
     tmem_ld_wait();
     if (in_range) {
+      // every lane writes its own row (rows are heads * D elements apart), so a store instruction costs one
+      // memory transaction per lane whatever its width: 32-byte stores halve the count
 #pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        uint4 w;
-        w.x = pack2<BF16>(__uint_as_float(o[v * 8 + 0]) * inv_l, __uint_as_float(o[v * 8 + 1]) * inv_l);
-        w.y = pack2<BF16>(__uint_as_float(o[v * 8 + 2]) * inv_l, __uint_as_float(o[v * 8 + 3]) * inv_l);
-        w.z = pack2<BF16>(__uint_as_float(o[v * 8 + 4]) * inv_l, __uint_as_float(o[v * 8 + 5]) * inv_l);
-        w.w = pack2<BF16>(__uint_as_float(o[v * 8 + 6]) * inv_l, __uint_as_float(o[v * 8 + 7]) * inv_l);
-        out_row[ch * 4 + v] = w;
+      for (int v = 0; v < 2; ++v) {
+        uint32_t w[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          w[e] = pack2<BF16>(__uint_as_float(o[v * 16 + 2 * e]) * inv_l, __uint_as_float(o[v * 16 + 2 * e + 1]) * inv_l);
+        if (wide_stores) {
+          st_global_v8(out_row + ch * 4 + v * 2, w);
+        } else {
+          out_row[ch * 4 + v * 2] = make_uint4(w[0], w[1], w[2], w[3]);
+          out_row[ch * 4 + v * 2 + 1] = make_uint4(w[4], w[5], w[6], w[7]);
+        }
       }
     }
   }
