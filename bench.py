@@ -35,7 +35,7 @@ WORKLOAD = "config2: causal MHA bf16, batch 4, 32 heads, seq 4096, head_dim 128 
 # dram__bytes_read.sum + dram__bytes_write.sum per attn_fwd_kernel launch: ncu capture of the same kernel on 16 of
 # the 128 (batch, head) units (51.7 MB, profiles/attn_fwd_kernel_b1_h16_s4096.md) scaled by 8 -- traffic grows in
 # proportion to the units, every unit reads its q, k, v once from DRAM.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 8 * 52.1e6
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 8 * 53.0e6
 
 
 def causal_flops(batch, heads, s, d):
