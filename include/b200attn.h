@@ -114,6 +114,10 @@ int b200_rotary_embedding_online(const int32_t* positions, void* query, void* ke
  * lse (optional, may be NULL): float32 [batch, heads, q_len], receives
  *   log2(sum_j exp(logit_ij)) (base-2 log-sum-exp of the scaled, capped, masked logits);
  *   the score passes below consume it.
+ * The kernel is a persistent grid whose CTAs draw query tiles from a counter; every launch takes a counter pair
+ * from a pool of 256 per GPU inside the library (returned to zero by the launch itself).  Launches in flight at
+ * the same time therefore use different pairs unless more than 256 are outstanding; a launch captured into a
+ * CUDA graph keeps the pair it drew at capture time.
  */
 int b200_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
                   int batch, int q_len, int kv_len, int heads, int kv_heads, int head_dim,
