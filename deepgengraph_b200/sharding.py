@@ -103,3 +103,62 @@ def scores_from_pieces(results, index: int = 1) -> torch.Tensor:
   """Stacks the score output `index` of run_sharded results into [units_local, kv_len] in unit order."""
   rows = [res[index].reshape(-1, res[index].size(-1)) for _, res in results]
   return torch.cat(rows, dim=0) if rows else torch.empty(0)
+
+
+# --------------------------------------------------------------------------------------------
+# Host-side failure detection.  The data path has no collective, so a failed rank can only hang
+# its peers at the optional score gather (or at a barrier of the caller).  Every rank therefore
+# reports the outcome of its local step to a key-value store (a torch.distributed Store, e.g. the
+# TCPStore of the process group) BEFORE entering the collective, and checks that all peers did:
+# a rank that raised, exited or never arrived is named in a PeerFailure raised on every surviving
+# rank within `timeout_s`, and no collective is launched.  Nothing here touches a GPU.
+# --------------------------------------------------------------------------------------------
+class PeerFailure(RuntimeError):
+  """Raised on a surviving rank: `failed` ranks reported an error, `missing` ranks never reported."""
+
+  def __init__(self, step, failed, missing):
+    self.step, self.failed, self.missing = step, dict(failed), list(missing)
+    parts = [f"rank {r} failed: {msg}" for r, msg in sorted(self.failed.items())]
+    parts += [f"rank {r} did not report within the time limit" for r in self.missing]
+    super().__init__(f"step {step}: " + "; ".join(parts))
+
+
+def report_step(store, rank: int, step, ok: bool = True, message: str = "") -> None:
+  """Publishes this rank's outcome of `step` (any hashable label) to the store."""
+  store.set(f"b200/step/{step}/rank/{rank}", "ok" if ok else "failed:" + message[:200])
+
+
+def check_peers(store, world: int, step, timeout_s: float = 30.0, poll_s: float = 0.02) -> None:
+  """Returns once every rank has reported `step` as ok; raises PeerFailure otherwise (after at most
+  `timeout_s` for ranks that never report)."""
+  import time
+  deadline = time.monotonic() + timeout_s
+  pending = set(range(world))
+  failed = {}
+  while pending:
+    for r in sorted(pending):
+      key = f"b200/step/{step}/rank/{r}"
+      if store.check([key]):
+        val = store.get(key).decode()
+        pending.discard(r)
+        if val != "ok":
+          failed[r] = val[len("failed:"):]
+    if failed:   # no point in waiting for the others: the step is lost
+      raise PeerFailure(step, failed, [])
+    if pending:
+      if time.monotonic() > deadline:
+        raise PeerFailure(step, failed, sorted(pending))
+      time.sleep(poll_s)
+
+
+def run_sharded_checked(fn, q, k, v, world: int, rank: int, store, step, extra=None, timeout_s: float = 30.0):
+  """run_sharded with failure detection: an exception in this rank's pieces is reported to the peers and
+  re-raised; otherwise the call returns only when every rank has finished `step`, or raises PeerFailure."""
+  try:
+    out = run_sharded(fn, q, k, v, world, rank, extra)
+  except Exception as e:   # noqa: BLE001 -- reported to the peers, then re-raised unchanged
+    report_step(store, rank, step, ok=False, message=f"{type(e).__name__}: {e}")
+    raise
+  report_step(store, rank, step)
+  check_peers(store, world, step, timeout_s)
+  return out

@@ -86,3 +86,50 @@ def _gather_worker(rank, world, port, n_units, kv_len, fail_rank):
 @pytest.mark.parametrize("world,n_units", [(2, 64), (2, 7), (3, 8)])
 def test_score_gather_on_gloo(world, n_units):
   mp.spawn(_gather_worker, args=(world, _free_port(), n_units, 33, 0), nprocs=world, join=True)
+
+
+# ---- host-side failure detection: a rank that raises, or never arrives, is reported by its peers ----
+def _failure_worker(rank, world, port, mode, result_dir):
+  import pathlib
+  import time
+  store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=__import__("datetime").timedelta(seconds=30))
+  B, S, H, D = 2, 16, 4, 8
+  g = torch.Generator().manual_seed(0)
+  q, k, v = (torch.randn(B, S, H, D, generator=g) for _ in range(3))
+
+  def fn(qs, ks, vs):
+    if mode == "raise" and rank == 1:
+      raise ValueError("injected failure in the local step")
+    return (qs + ks + vs,)
+
+  outcome = "none"
+  try:
+    if mode == "absent" and rank == 1:
+      time.sleep(3.0)          # never reports within the peers' time limit, then leaves
+      outcome = "left"
+    else:
+      t0 = time.monotonic()
+      res = sh.run_sharded_checked(fn, q, k, v, world, rank, store, step="s0", timeout_s=1.0)
+      outcome = f"ok:{len(res)}"
+  except sh.PeerFailure as e:
+    outcome = f"peer_failure:failed={sorted(e.failed)}:missing={e.missing}:{time.monotonic() - t0:.1f}s"
+  except ValueError as e:
+    outcome = f"own_error:{e}"
+  pathlib.Path(result_dir, f"rank{rank}.txt").write_text(outcome)
+  if rank == 0:
+    time.sleep(3.5 if mode == "absent" else 0.5)   # the store's host outlives its clients
+
+
+@pytest.mark.parametrize("mode,world", [("ok", 2), ("raise", 3), ("absent", 2)])
+def test_failed_or_absent_rank_is_reported_without_a_collective(tmp_path, mode, world):
+  mp.spawn(_failure_worker, args=(world, _free_port(), mode, str(tmp_path)), nprocs=world, join=True)
+  got = {r: (tmp_path / f"rank{r}.txt").read_text() for r in range(world)}
+  if mode == "ok":
+    assert all(v.startswith("ok:") for v in got.values()), got
+  elif mode == "raise":
+    assert got[1].startswith("own_error:injected failure"), got
+    for r in (0, 2):
+      assert got[r].startswith("peer_failure:failed=[1]:missing=[]"), got
+  else:
+    assert got[1] == "left" and got[0].startswith("peer_failure:failed=[]:missing=[1]"), got
+    assert float(got[0].rsplit(":", 1)[1][:-1]) < 2.5, got   # reported at the time limit, not when the rank left
