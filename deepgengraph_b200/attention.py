@@ -18,6 +18,8 @@ import math
 
 import torch
 
+from .tracing import traced
+
 from . import _lib
 from .native_ops import _dtype_code, _require_cuda, _stream_ptr
 
@@ -242,16 +244,19 @@ def _(q, k, v, causal, scale):
 # ----------------------------------------------------------------------------------------------
 # public functions
 # ----------------------------------------------------------------------------------------------
+@traced
 def attn_fwd(q, k, v, causal=True, window=-1, softcap=0.0, scale=None):
   """softmax(mask(softcap(q k^T * scale))) v   (kernels/attn.py:18-34, kernels/gemma2.py:19-38)."""
   return _op_attn_fwd(q, k, v, bool(causal), int(window), float(softcap), float(scale or 0.0))
 
 
+@traced
 def attn_fwd_with_lse(q, k, v, causal=True, window=-1, softcap=0.0, scale=None):
   """attn_fwd plus the base-2 log-sum-exp of every row of scaled logits, float32 [B, H, Sq]."""
   return _attn_fwd_impl(q, k, v, causal, window, softcap, scale, want_lse=True)
 
 
+@traced
 def attn_score_fwd(q, k, v, want_sq=False, causal=True, window=-1, softcap=0.0, scale=None):
   """Attention output + per-key column sums of the fp32 probabilities (kernels/h2o.py:35-38);
   want_sq adds the column sums of the squared probabilities (kernels/roco.py:42-48)."""
@@ -259,24 +264,28 @@ def attn_score_fwd(q, k, v, want_sq=False, causal=True, window=-1, softcap=0.0, 
   return op(q, k, v, bool(causal), int(window), float(softcap), float(scale or 0.0))
 
 
+@traced
 def attn_kf_fwd(q, k, v, exp_rand, tau=1.5, causal=True, scale=None):
   """Attention output + KeyFormer score: column sums of softmax((logits - log(exp_rand)) / tau)
   (kernels/kf.py:36-42)."""
   return _op_attn_kf_fwd(q, k, v, exp_rand, float(tau), bool(causal), float(scale or 0.0))
 
 
+@traced
 def attn_snapkv_fwd(q, k, v, kernel_size=5, causal=True, scale=None):
   """Attention output + column sums average-pooled over a window of `kernel_size` keys, zero padded
   (kernels/snapkv.py:36-38)."""
   return _op_attn_snapkv_fwd(q, k, v, int(kernel_size), bool(causal), float(scale or 0.0))
 
 
+@traced
 def attn_corm_fwd(q, k, v, causal=True, scale=None):
   """Attention output + bool [B, H, Skv]: does any query i attend to the key with probability >= 1 / (i + 1)
   (kernels/corm.py:35-37; the thresholds of Corm.prepare, kernels/corm.py:47-49, are evaluated in the kernel)."""
   return _op_attn_corm_fwd(q, k, v, bool(causal), float(scale or 0.0))
 
 
+@traced
 def kv_evict_topk(score, k, v, budget, return_indices=False):
   """KV-cache eviction step of the reference's model glue (models/h2o.py:51-57, models/kf.py:54-60): per (batch,
   head) keep the `budget` keys with the largest score, in position order.
@@ -301,6 +310,7 @@ def kv_evict_topk(score, k, v, budget, return_indices=False):
   return (kv_cache, idx) if return_indices else kv_cache
 
 
+@traced
 def kv_evict_roco(score, score_sq, k, v, q_len, budget, recent, return_indices=False):
   """RoCo's KV-cache eviction (models/roco.py:52-66): keep the `recent` keys whose attention probabilities vary
   most over the queries (largest std, from the column sums of p and p^2) and, of the rest, the `budget` keys with

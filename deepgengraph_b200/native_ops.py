@@ -14,6 +14,8 @@ raise instead of launching on bad input.
 """
 import torch
 
+from .tracing import traced
+
 from . import _lib
 
 _DTYPES = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
@@ -40,6 +42,7 @@ def _stream_ptr(dev):
   return torch.cuda.current_stream(dev).cuda_stream
 
 
+@traced
 def rms_norm(out, input, weight, epsilon):
   """out = T(input * rsqrt(mean(input^2, -1) + epsilon)) * weight   (csrc/norm.cu:34-56)."""
   where = "rms_norm"
@@ -58,6 +61,7 @@ def rms_norm(out, input, weight, epsilon):
   _lib.check(st, where)
 
 
+@traced
 def fused_add_rms_norm(input, residual, weight, epsilon):
   """residual += input; input = rms_norm(residual) * weight, both in place (csrc/norm.cu:59-83)."""
   where = "fused_add_rms_norm"
@@ -93,16 +97,19 @@ def _act_and_mul(fn_name, out, input):
   _lib.check(st, fn_name)
 
 
+@traced
 def silu_and_mul(out, input):
   """out[..., i] = T(silu(input[..., i])) * input[..., d + i]   (csrc/activation.cu:6-34)."""
   _act_and_mul("silu_and_mul", out, input)
 
 
+@traced
 def gelu_tanh_and_mul(out, input):
   """out[..., i] = T(gelu_tanh(input[..., i])) * input[..., d + i] (GeGLU gate)."""
   _act_and_mul("gelu_tanh_and_mul", out, input)
 
 
+@traced
 def rotary_embedding_online(positions, query, key, head_size, rope_theta):
   """In-place NeoX rotary embedding of query [T, H*D] and key [T, Hk*D] (csrc/pos_encoding.cu:64-113,180-199).
 

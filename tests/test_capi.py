@@ -60,3 +60,17 @@ def test_bad_arguments_are_rejected_without_a_gpu():
   assert lib.b200_attn_score(p, p, p, p, p, None, None, 0, 1, 128, 128, 2, 128, _lib.BF16, 1, 0, 0.0, 0.088, None) == 5
   assert lib.b200_attn_score(p, p, p, p, p, None, p, need - 1, 1, 128, 128, 2, 128, _lib.BF16, 1, 0, 0.0, 0.088, None) == 5
   assert lib.b200_attn_kf_score(p, p, p, p, p, p, p, need, 1, 128, 128, 2, 256, _lib.BF16, 1, 1.0, 0.088, None) == 4
+
+
+def test_tracing_wrapper_is_transparent_when_off():
+  from deepgengraph_b200 import attention, native_ops, tracing
+  assert attention.attn_fwd.__name__ == "attn_fwd" and native_ops.rms_norm.__name__ == "rms_norm"
+  calls = []
+
+  @tracing.traced
+  def probe(x, y=2):
+    calls.append((x, y))
+    return x + y
+
+  tracing.enable(False)
+  assert probe(1, y=3) == 4 and calls == [(1, 3)]

@@ -70,3 +70,16 @@ def test_custom_ops_are_registered_with_fake_kernels(cuda_device):
     fq = torch.empty(1, 128, 2, 128, device="cuda", dtype=torch.bfloat16)
     o, s = torch.ops.b200attn.attn_score_fwd(fq, fq, fq, True, -1, 0.0, 0.0)
     assert tuple(o.shape) == (1, 128, 2, 128) and tuple(s.shape) == (1, 2, 128) and s.dtype == torch.float32
+
+
+def test_nvtx_ranges_do_not_change_results(cuda_device):
+  from deepgengraph_b200 import attention as att, tracing
+  g = torch.Generator().manual_seed(0)
+  q, k, v = (torch.randn(1, 256, 2, 128, generator=g).to(torch.bfloat16).to(cuda_device) for _ in range(3))
+  want = att.attn_fwd(q, k, v)
+  tracing.enable(True)
+  try:
+    got = att.attn_fwd(q, k, v)
+  finally:
+    tracing.enable(False)
+  assert torch.equal(got, want)
