@@ -6,7 +6,7 @@ reference kernels themselves on the same device.  No reference source is copied:
 they lie.  Flags follow the reference's setup.py:20-38 (-O3 --use_fast_math -std=c++17, half/bf16 operators
 enabled); only the architecture differs (the reference builds for 8.0/8.6/9.0).
 
-    python oracle/build_ref.py [/root/reference]
+    python oracle/build_ref.py [<reference tree>]      (default: $B200_REFERENCE_ROOT)
 """
 import os
 import subprocess
@@ -18,7 +18,10 @@ OUT_DIR = os.path.join(HERE, "_ref")
 OUT = os.path.join(OUT_DIR, "_csrc_ref.so")
 
 
-def build(ref_root="/root/reference", force=False):
+DEFAULT_REF_ROOT = os.environ.get("B200_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
+
+
+def build(ref_root=DEFAULT_REF_ROOT, force=False):
   srcs = [os.path.join(ref_root, "csrc", f) for f in ("norm.cu", "activation.cu", "pos_encoding.cu", "ffi.cpp")]
   if not all(os.path.exists(s) for s in srcs):
     return None
@@ -62,4 +65,4 @@ def build(ref_root="/root/reference", force=False):
 
 
 if __name__ == "__main__":
-  print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", force=True))
+  print(build(sys.argv[1] if len(sys.argv) > 1 else DEFAULT_REF_ROOT, force=True))

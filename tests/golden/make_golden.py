@@ -2,7 +2,7 @@
 (deepgengraph_exp/cases/kernels/*.py) on the seeded inputs of cases.py, in fp32 on CPU.
 
 Run inside the build container, where the reference tree is mounted:
-    python tests/golden/make_golden.py [/root/reference]
+    python tests/golden/make_golden.py [<reference tree>]      (default: $B200_REFERENCE_ROOT)
 The GPU box has no reference tree; it only reads the committed .npz files.
 
 Each file holds: `out_rows` (every ROW_STRIDE-th query row of the attention output, fp32),
@@ -31,7 +31,7 @@ def load_reference(ref_root):
 
 
 def main():
-  ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+  ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("B200_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
   zoo = load_reference(ref_root)
   for name, c in cases.CASES.items():
     inp = cases.make_inputs(name, torch.float32)
