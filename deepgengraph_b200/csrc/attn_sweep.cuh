@@ -40,6 +40,9 @@ struct SweepParams {
   int batch, heads, q_len, kv_len, delta, causal, window;
   int lse_stride, kv_pad, n_chunks, chunk_blocks;
   int kv_group;         // query heads per K/V head (the key operand of head h is K head h / kv_group)
+  // stationary operand as plain memory (configurations that keep it in TMEM load it with ordinary loads):
+  const uint16_t* a_base;   // K (column-sum sweeps) or Q (row-LSE sweep), [batch, rows, a_heads, 128]
+  int a_rows, a_heads;
   float scale_log2, cap_in, cap_out, inv_tau;
 };
 
@@ -49,13 +52,19 @@ struct SweepCfg {
   static constexpr int D = 128, BM = 128;
   static constexpr bool NOISE = MODE != SWEEP_COLSUM;
   static constexpr bool LSE_IN = MODE != SWEEP_KF_ROWLSE;
-  static constexpr int A_BYTES = BM * D * 2;
+  // BX = 64: the stationary tile lives in TMEM (64 columns beside the two 64-column product tiles) and is the
+  // A operand of the MMAs, which then read only the streamed operand from shared memory -- with both operands
+  // in shared memory the M128 x N64 MMAs ask for 192 B/clk of a 128 B/clk port, and every shared-memory access
+  // of the compute warps (noise, normalisers, barrier probes) queues behind them.
+  static constexpr bool A_TMEM = BX == 64;
+  static constexpr int A_BYTES = A_TMEM ? 0 : BM * D * 2;
+  static constexpr int A_COL = 2 * BX;                                  // first TMEM column of the stationary tile
   static constexpr int X_STAGE_BYTES = BX * D * 2;
   static constexpr int NOISE_BYTES = NOISE ? BM * BX * 4 : 0;
   static constexpr int LSE_BYTES = LSE_IN ? BX * 4 : 0;
   static constexpr int N_STAGE_BYTES = NOISE_BYTES + LSE_BYTES;       // auxiliary ring read by the compute warps
   static constexpr int N_STAGE_STRIDE = (N_STAGE_BYTES + 1023) / 1024 * 1024;
-  static constexpr int TMEM_COLS = 2 * BX < 32 ? 32 : 2 * BX;        // two S tiles (power of two for BX in {64,128})
+  static constexpr int TMEM_COLS = A_TMEM ? 256 : 2 * BX;               // two product tiles (+ the stationary tile)
   static constexpr int THREADS = 6 * 32;
   static constexpr int BAR_A_FULL = 0;
   static constexpr int BAR_X_FULL = 1;
@@ -87,11 +96,13 @@ template <class Cfg>
 __device__ __forceinline__ void sweep_producer(const SweepCtx<Cfg>& c, const SweepParams& p, const CUtensorMap* tm_a,
                                                const CUtensorMap* tm_x, const CUtensorMap* tm_n) {
   constexpr int ST = Cfg::STAGES, BX = Cfg::BX;
-  mbar_expect_tx(&c.bars[Cfg::BAR_A_FULL], Cfg::A_BYTES);
+  if constexpr (!Cfg::A_TMEM) {
+    mbar_expect_tx(&c.bars[Cfg::BAR_A_FULL], Cfg::A_BYTES);
 #pragma unroll
-  for (int ks = 0; ks < 2; ++ks)
-    tma_load_4d(c.sA + ks * (Cfg::BM * 128), tm_a, &c.bars[Cfg::BAR_A_FULL], ks * 64,
-                Cfg::MODE == SWEEP_KF_ROWLSE ? c.h : c.h / p.kv_group, c.a0, c.b);
+    for (int ks = 0; ks < 2; ++ks)
+      tma_load_4d(c.sA + ks * (Cfg::BM * 128), tm_a, &c.bars[Cfg::BAR_A_FULL], ks * 64,
+                  Cfg::MODE == SWEEP_KF_ROWLSE ? c.h : c.h / p.kv_group, c.a0, c.b);
+  }
   bool ok = true;
   int n_issued = 0;
   for (int blk = c.blk_lo; blk < c.blk_hi; ++blk) {
@@ -182,10 +193,19 @@ __device__ __forceinline__ void sweep_mma(const SweepCtx<Cfg>& c) {
       for (int kk = 0; kk < 8; ++kk) {
         const uint32_t a_off = (uint32_t)(((kk / 4) * (128 * 128) + (kk % 4) * 32) >> 4);
         const uint32_t b_off = (uint32_t)(((kk / 4) * (BX * 128) + (kk % 4) * 32) >> 4);
-        if (kk == 0)
-          umma_ss_c<IDESC, 0>(d_tmem, a_lo + a_off, b0 + b_off, desc_hi);
-        else
-          umma_ss_c<IDESC, 1>(d_tmem, a_lo + a_off, b0 + b_off, desc_hi);
+        if constexpr (Cfg::A_TMEM) {
+          // stationary tile in TMEM: 16 dims (one K step) = 8 columns of packed 16-bit pairs
+          const uint32_t a_tmem = c.tmem_base + Cfg::A_COL + kk * 8;
+          if (kk == 0)
+            umma_ts_c<IDESC, 0>(d_tmem, a_tmem, b0 + b_off, desc_hi);
+          else
+            umma_ts_c<IDESC, 1>(d_tmem, a_tmem, b0 + b_off, desc_hi);
+        } else {
+          if (kk == 0)
+            umma_ss_c<IDESC, 0>(d_tmem, a_lo + a_off, b0 + b_off, desc_hi);
+          else
+            umma_ss_c<IDESC, 1>(d_tmem, a_lo + a_off, b0 + b_off, desc_hi);
+        }
       }
       umma_commit(&c.bars[Cfg::BAR_T_FULL + tb]);
       umma_commit(&c.bars[Cfg::BAR_X_EMPTY + st]);
@@ -422,7 +442,7 @@ attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     for (int i = 0; i < Cfg::NUM_BARS; ++i) {
       const bool warp_count = (i >= Cfg::BAR_N_EMPTY && i < Cfg::BAR_N_EMPTY + STAGES) ||
                               (i >= Cfg::BAR_T_EMPTY && i < Cfg::BAR_T_EMPTY + 2);
-      mbar_init(&c.bars[i], warp_count ? 4u : 1u);
+      mbar_init(&c.bars[i], (warp_count || (Cfg::A_TMEM && i == Cfg::BAR_A_FULL)) ? 4u : 1u);
     }
     *c.abort_flag = 0;
     fence_mbar_init();
@@ -442,6 +462,32 @@ attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   c.tmem_base = *tmem_slot;
 
   if (warp < 4) {
+    if constexpr (Cfg::A_TMEM) {
+      // thread r copies row r of the stationary tile (256 contiguous bytes) from global memory into TMEM lane r;
+      // a 32-bit TMEM column holds two consecutive 16-bit elements, which is the order they have in memory
+      const int row = c.a0 + (int)threadIdx.x;
+      const int a_head = MODE == SWEEP_KF_ROWLSE ? c.h : c.h / p.kv_group;
+      const uint4* src = reinterpret_cast<const uint4*>(
+          p.a_base + (((int64_t)c.b * p.a_rows + row) * p.a_heads + a_head) * 128);
+      const uint32_t dst = c.tmem_base + ((uint32_t)(warp * 32) << 16) + Cfg::A_COL;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t w[32];
+#pragma unroll
+        for (int v8 = 0; v8 < 8; ++v8) {
+          const uint4 x = row < p.a_rows ? __ldg(src + half * 8 + v8) : make_uint4(0u, 0u, 0u, 0u);
+          w[4 * v8] = x.x;
+          w[4 * v8 + 1] = x.y;
+          w[4 * v8 + 2] = x.z;
+          w[4 * v8 + 3] = x.w;
+        }
+        tmem_st32(dst + half * 32, w);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&c.bars[Cfg::BAR_A_FULL]);
+    }
     if constexpr (MODE == SWEEP_KF_ROWLSE)
       sweep_compute_rowlse<Cfg>(c, p);
     else
@@ -486,7 +532,16 @@ int static_score_scratch(void** out);
 #ifndef B200_SWEEP_CHUNK
 #define B200_SWEEP_CHUNK 32
 #endif
-constexpr int kSweepChunkBlocks = B200_SWEEP_CHUNK;   // streamed blocks per CTA in the column-sum sweeps
+constexpr int kSweepChunkBlocks = B200_SWEEP_CHUNK;
+#ifndef B200_COLSUM_BX
+#define B200_COLSUM_BX 128
+#endif
+#ifndef B200_COLSUM_STAGES
+#define B200_COLSUM_STAGES 2
+#endif
+#ifndef B200_KF_STAGES
+#define B200_KF_STAGES 3
+#endif   // streamed blocks per CTA in the column-sum sweeps
 
 struct ScoreWorkspace {
   int lse_stride, kv_pad, n_chunks_colsum, n_chunks_kf;
@@ -603,7 +658,7 @@ inline int attn_score_impl(const void* q, const void* k, const void* v, void* ou
   const bool bf16 = dtype == B200_BF16;
   CUtensorMap ta, tx, tn;
   if ((rc = make_bshd_tensor_map(&ta, k, batch, kv_len, kv_heads, head_dim, 128, bf16)) != B200_OK) return rc;
-  if ((rc = make_bshd_tensor_map(&tx, q, batch, q_len, heads, head_dim, 128, bf16)) != B200_OK) return rc;
+  if ((rc = make_bshd_tensor_map(&tx, q, batch, q_len, heads, head_dim, B200_COLSUM_BX, bf16)) != B200_OK) return rc;
   tn = ta;  // unused
 
   SweepParams p;
@@ -621,7 +676,10 @@ inline int attn_score_impl(const void* q, const void* k, const void* v, void* ou
   p.lse_stride = w.lse_stride;
   p.kv_pad = w.kv_pad;
   p.n_chunks = w.n_chunks_colsum;
-  p.chunk_blocks = kSweepChunkBlocks;
+  p.chunk_blocks = kSweepChunkBlocks * (128 / B200_COLSUM_BX);
+  p.a_base = static_cast<const uint16_t*>(k);
+  p.a_rows = kv_len;
+  p.a_heads = kv_heads;
   p.kv_group = group;
   const float kLog2e = 1.4426950408889634f;
   p.scale_log2 = scale * kLog2e;
@@ -632,7 +690,8 @@ inline int attn_score_impl(const void* q, const void* k, const void* v, void* ou
   const bool cap = softcap > 0.f, sq = score_sq != nullptr;
   const int gy = w.kv_pad / 128;
 
-#define B200_SWEEP0(BF, CAP, AUXV) launch_sweep<SWEEP_COLSUM, 128, 2, BF, CAP, AUXV>(ta, tx, tn, p, p.n_chunks, gy, stream)
+#define B200_SWEEP0(BF, CAP, AUXV) \
+  launch_sweep<SWEEP_COLSUM, B200_COLSUM_BX, B200_COLSUM_STAGES, BF, CAP, AUXV>(ta, tx, tn, p, p.n_chunks, gy, stream)
   if (corm_flags != nullptr)
     rc = bf16 ? B200_SWEEP0(true, false, AUX_CORM) : B200_SWEEP0(false, false, AUX_CORM);
   else if (bf16)
@@ -702,16 +761,21 @@ inline int attn_kf_impl(const void* q, const void* k, const void* v, const float
   p.scale_log2 = scale * 1.4426950408889634f;
   p.inv_tau = 1.0f / tau;
   p.kv_group = 1;
+  p.a_heads = heads;
 
   // sweep 1: Lz_i = log2 sum_j exp2(z_ij), one CTA per 128 queries
   const int q_tiles = (q_len + 127) / 128;
-  rc = bf16 ? launch_sweep<SWEEP_KF_ROWLSE, 64, 3, true, false, false>(tq128, tk64, tn_rows128, p, 1, q_tiles, stream)
-            : launch_sweep<SWEEP_KF_ROWLSE, 64, 3, false, false, false>(tq128, tk64, tn_rows128, p, 1, q_tiles, stream);
+  p.a_base = static_cast<const uint16_t*>(q);
+  p.a_rows = q_len;
+  rc = bf16 ? launch_sweep<SWEEP_KF_ROWLSE, 64, B200_KF_STAGES, true, false, false>(tq128, tk64, tn_rows128, p, 1, q_tiles, stream)
+            : launch_sweep<SWEEP_KF_ROWLSE, 64, B200_KF_STAGES, false, false, false>(tq128, tk64, tn_rows128, p, 1, q_tiles, stream);
   if (rc != B200_OK) return rc;
   // sweep 2: per-key sums of exp2(z_ij - Lz_i)
   const int gy = w.kv_pad / 128;
-  rc = bf16 ? launch_sweep<SWEEP_KF_COLSUM, 64, 3, true, false, false>(tk128, tq64, tn_rows64, p, p.n_chunks, gy, stream)
-            : launch_sweep<SWEEP_KF_COLSUM, 64, 3, false, false, false>(tk128, tq64, tn_rows64, p, p.n_chunks, gy, stream);
+  p.a_base = static_cast<const uint16_t*>(k);
+  p.a_rows = kv_len;
+  rc = bf16 ? launch_sweep<SWEEP_KF_COLSUM, 64, B200_KF_STAGES, true, false, false>(tk128, tq64, tn_rows64, p, p.n_chunks, gy, stream)
+            : launch_sweep<SWEEP_KF_COLSUM, 64, B200_KF_STAGES, false, false, false>(tk128, tq64, tn_rows64, p, p.n_chunks, gy, stream);
   if (rc != B200_OK) return rc;
 
   dim3 rgrid((kv_len + 255) / 256, batch * heads);
