@@ -284,9 +284,14 @@ __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, con
 
   for (int blk = c.blk_lo; blk < c.blk_hi; ++blk) {
     const int n = blk - c.blk_lo, st = n % ST, tb = n & 1;
+    [[maybe_unused]] const bool tl_on = threadIdx.x == 0;
+    [[maybe_unused]] const int tl_base = (n & 63) * 8;
+    if (tl_on) B200_TL(tl_base + 0);
     if (!mbar_wait(&c.bars[Cfg::BAR_T_FULL + tb], (n >> 1) & 1, c.abort_flag, WAIT_T_FULL)) return;
+    if (tl_on) B200_TL(tl_base + 1);
     if (!mbar_wait(&c.bars[Cfg::BAR_N_FULL + st], (n / ST) & 1, c.abort_flag, WAIT_N_FULL)) return;
     tc_fence_after();
+    if (tl_on) B200_TL(tl_base + 2);
     const uint8_t* nst = c.sN + st * Cfg::N_STAGE_STRIDE;
     const float* lse_s = reinterpret_cast<const float*>(nst + Cfg::NOISE_BYTES);
     const float* noise_col = reinterpret_cast<const float*>(nst + warp_q * (BX * 128)) + lane;  // + i * 32
@@ -307,6 +312,7 @@ __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, con
         chunk_body(std::true_type{}, sr[ch & 1], ch, lse_s, noise_col, lo_c, hi_c, (float)(i0 + 1));
       else
         chunk_body(std::false_type{}, sr[ch & 1], ch, lse_s, noise_col, lo_c, hi_c, (float)(i0 + 1));
+      if (tl_on && ch < 4) B200_TL(tl_base + 3 + ch);
     }
     // this TMEM buffer and this auxiliary stage may be refilled
     tc_fence_before();
@@ -315,6 +321,7 @@ __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, con
       mbar_arrive(&c.bars[Cfg::BAR_T_EMPTY + tb]);
       mbar_arrive(&c.bars[Cfg::BAR_N_EMPTY + st]);
     }
+    if (tl_on) B200_TL(tl_base + 7);
   }
   const float acc0 = acc2.x, acc1 = acc2.y, sq0 = sq2.x, sq1 = sq2.y;
   const int64_t off = ((int64_t)c.bh * p.n_chunks + chunk) * p.kv_pad + key;
@@ -399,6 +406,7 @@ attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   __syncthreads();
   if (s_skip != 0) return;
 
+  B200_TL_INIT();
   SweepCtx<Cfg> c;
   c.sA = smem;
   c.sX = c.sA + Cfg::A_BYTES;
@@ -500,6 +508,7 @@ attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(c.tmem_base, Cfg::TMEM_COLS);
+  B200_TL_FLUSH();
 }
 
 // Adds the per-chunk partial vectors in chunk order: out[bh][j] = mul * sum_c partial[bh][c][j].
