@@ -59,6 +59,8 @@ def _attn_fwd_impl(q, k, v, causal, window, softcap, scale, want_lse=False):
     scale = 1.0 / math.sqrt(D)
   out = torch.empty((B, Sq, H, D), dtype=q.dtype, device=dev)
   lse = torch.empty((B, H, Sq), dtype=torch.float32, device=dev) if want_lse else None
+  if B == 0 or Sq == 0:   # empty batch / no queries: nothing to launch (the torch reference returns empty tensors)
+    return (out, lse) if want_lse else out
   with torch.cuda.device(dev):
     if q.is_contiguous() and k.is_contiguous() and v.is_contiguous():
       st = _lib.load().b200_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
@@ -96,6 +98,11 @@ def _attn_score_impl(q, k, v, want_sq, causal, window, softcap, scale):
   out = torch.empty_like(q)
   score = torch.empty((B, Hk, Skv), dtype=torch.float32, device=dev)
   score_sq = torch.empty((B, H, Skv), dtype=torch.float32, device=dev) if want_sq else None
+  if B == 0 or Sq == 0:   # no queries: every column sum is an empty sum
+    score.zero_()
+    if want_sq:
+      score_sq.zero_()
+    return (out, score, score_sq) if want_sq else (out, score)
   ws, nbytes = _workspace(dev, B, Sq, Skv, H)
   if H != Hk:
     # grouped-query attention: mean over the query heads of a K/V head, then the column sum (kernels/roco.py:39-40)

@@ -221,6 +221,15 @@ def test_many_tiny_tiles_per_cta(cuda_device, case):
     assert torch.equal(att.attn_fwd(qd, kd, vd, causal=True, window=window), out)
 
 
+def test_empty_batch_returns_empty_tensors(cuda_device):
+  # the reference's torch modules return empty tensors for an empty batch; nothing is launched here
+  q = torch.empty(0, 256, 4, 128, dtype=torch.bfloat16, device=cuda_device)
+  out, lse = att.attn_fwd_with_lse(q, q, q)
+  assert out.shape == (0, 256, 4, 128) and lse.shape == (0, 4, 256)
+  out, score, score_sq = att.attn_score_fwd(q, q, q, want_sq=True)
+  assert out.shape == q.shape and score.shape == (0, 4, 256) and score_sq.shape == (0, 4, 256)
+
+
 def test_host_validation(cuda_device):
   q, k, v = (t.to(cuda_device) for t in _qkv(1, 128, 128, 2, 2, 128, torch.bfloat16))
   with pytest.raises(TypeError):
