@@ -230,6 +230,26 @@ def test_empty_batch_returns_empty_tensors(cuda_device):
   assert out.shape == q.shape and score.shape == (0, 4, 256) and score_sq.shape == (0, 4, 256)
 
 
+def test_long_sequence_32k(cuda_device):
+  # 256 query tiles of up to 512 key blocks per head: long barrier-phase and ring-counter runs inside one CTA.
+  # The oracle is evaluated for a few query rows only (each row is independent of the others).
+  B, S, H, D = 1, 32768, 2, 128
+  q, k, v = _qkv(B, S, S, H, H, D, torch.bfloat16, seed=61)
+  out = att.attn_fwd(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device)).float().cpu()
+  assert torch.isfinite(out).all()
+  rows = torch.tensor([0, 1, 127, 128, 4095, 20000, 32767 - 128, 32767])
+  scale = D ** -0.5
+  for h in range(H):
+    logits = (q[0, rows, h].float() @ k[0, :, h].float().T) * scale                  # [rows, S]
+    logits = logits.masked_fill(torch.arange(S)[None, :] > rows[:, None], float("-inf"))
+    p = torch.softmax(logits, dim=-1).to(torch.bfloat16).float()
+    ref = p @ v[0, :, h].float()
+    torch.testing.assert_close(out[0, rows, h], ref, **TOL)
+  ones = torch.ones(B, S, H, D, dtype=torch.bfloat16, device=cuda_device)
+  o1 = att.attn_fwd(q.to(cuda_device), k.to(cuda_device), ones).float()
+  torch.testing.assert_close(o1, torch.ones_like(o1), rtol=1e-2, atol=1e-2)
+
+
 def test_host_validation(cuda_device):
   q, k, v = (t.to(cuda_device) for t in _qkv(1, 128, 128, 2, 2, 128, torch.bfloat16))
   with pytest.raises(TypeError):
