@@ -250,6 +250,17 @@ def test_long_sequence_32k(cuda_device):
   torch.testing.assert_close(o1, torch.ones_like(o1), rtol=1e-2, atol=1e-2)
 
 
+def test_rescale_path_in_ctas_that_walk_several_tiles(cuda_device):
+  # growing key norms force repeated rescales of the O accumulator; with 400 tiles every persistent CTA meets them
+  # in its second tile too, where the O barriers are addressed by the CTA-wide block counter
+  B, S, H, D = 2, 2560, 10, 128
+  q, k, v = _qkv(B, S, S, H, H, D, torch.bfloat16, seed=71)
+  k = (k.float() * torch.linspace(0.2, 5.0, S)[None, :, None, None]).to(torch.bfloat16)
+  ref = rm.attention_ref(q, k, v, causal=True, head_chunk=5)["out"]
+  out = att.attn_fwd(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), causal=True)
+  torch.testing.assert_close(out.float().cpu(), ref, **TOL)
+
+
 def test_host_validation(cuda_device):
   q, k, v = (t.to(cuda_device) for t in _qkv(1, 128, 128, 2, 2, 128, torch.bfloat16))
   with pytest.raises(TypeError):
