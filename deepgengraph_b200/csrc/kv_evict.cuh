@@ -172,18 +172,24 @@ kv_evict_topk_kernel(const float* __restrict__ score, const uint8_t* __restrict_
                                           &s_remaining, &need_equal);
 
   // ---- ordered compaction: selected indices in ascending order ----
-  int sel_base = 0, eq_base = 0;
+  // Selected = every key above the threshold plus the first `need_equal` keys equal to it, so the output position
+  // of key i is (#greater before i) + min(#equal before i, need_equal): one block scan of the two counts packed
+  // into one word (greater in the low half, equal in the high half; at most 256 of each per step).
+  int gt_base = 0, eq_base = 0;
   for (int i0 = 0; i0 < seq; i0 += kEvictThreads) {
     const int i = i0 + threadIdx.x;
     const uint32_t u = i < seq ? key_of(i) : 0u;
+    const int is_gt = (i < seq && u > thr) ? 1 : 0;
     const int is_eq = (i < seq && u == thr) ? 1 : 0;
-    int eq_total, sel_total;
-    const int eq_before = eq_base + block_exclusive_scan(is_eq, warp_sums, &eq_total);
-    const int is_sel = (i < seq && (u > thr || (is_eq && eq_before < need_equal))) ? 1 : 0;
-    const int pos = sel_base + block_exclusive_scan(is_sel, warp_sums, &sel_total);
-    if (is_sel && pos < budget) s_idx[pos] = i;
-    sel_base += sel_total;
-    eq_base += eq_total;
+    int total;
+    const int before = block_exclusive_scan(is_gt | (is_eq << 16), warp_sums, &total);
+    const int gt_before = gt_base + (before & 0xffff), eq_before = eq_base + (before >> 16);
+    if (is_gt || (is_eq && eq_before < need_equal)) {
+      const int pos = gt_before + min(eq_before, need_equal);
+      if (pos < budget) s_idx[pos] = i;
+    }
+    gt_base += total & 0xffff;
+    eq_base += total >> 16;
   }
   __syncthreads();
 
@@ -272,20 +278,25 @@ kv_evict_roco_kernel(const float* __restrict__ score, const float* __restrict__ 
                                &s_prefix, &s_remaining, &need_eq_b);
 
   // ---- ordered compaction of A u B ----
-  int sel_base = 0, eq_base = 0;
+  // "sure" keys (in A, or above the B threshold) and keys equal to the B threshold are counted in one packed scan;
+  // position of key i = (#sure before i) + min(#equal before i, need_eq_b), as in the top-k kernel
+  int sure_base = 0, eq_base = 0;
   for (int i0 = 0; i0 < seq; i0 += kEvictThreads) {
     const int i = i0 + threadIdx.x;
     const bool a = i < seq && in_a[i] != 0;
-    const uint32_t u = (i < seq && !a && budget > 0) ? mean_key(i) : 0u;
-    const int is_eq = (i < seq && !a && budget > 0 && u == thr_b) ? 1 : 0;
-    int eq_total, sel_total;
-    const int eq_before = eq_base + block_exclusive_scan(is_eq, warp_sums, &eq_total);
-    const bool in_b = i < seq && !a && budget > 0 && (u > thr_b || (is_eq && eq_before < need_eq_b));
-    const int is_sel = (a || in_b) ? 1 : 0;
-    const int pos = sel_base + block_exclusive_scan(is_sel, warp_sums, &sel_total);
-    if (is_sel && pos < keep) s_idx[pos] = i;
-    sel_base += sel_total;
-    eq_base += eq_total;
+    const bool cand = i < seq && !a && budget > 0;
+    const uint32_t u = cand ? mean_key(i) : 0u;
+    const int is_sure = (a || (cand && u > thr_b)) ? 1 : 0;
+    const int is_eq = (cand && u == thr_b) ? 1 : 0;
+    int total;
+    const int before = block_exclusive_scan(is_sure | (is_eq << 16), warp_sums, &total);
+    const int sure_before = sure_base + (before & 0xffff), eq_before = eq_base + (before >> 16);
+    if (is_sure || (is_eq && eq_before < need_eq_b)) {
+      const int pos = sure_before + min(eq_before, need_eq_b);
+      if (pos < keep) s_idx[pos] = i;
+    }
+    sure_base += total & 0xffff;
+    eq_base += total >> 16;
   }
   __syncthreads();
 
