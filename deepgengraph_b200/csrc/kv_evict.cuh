@@ -6,11 +6,12 @@
 //     k_cache = gather(k, idx); v_cache = gather(v, idx); kv_cache = cat([k_cache, v_cache], dim=1)
 // i.e. the result only depends on the SET of the top-`budget` keys; it is emitted in ascending key order.
 //
-// One to eight CTAs per (batch, head): a 4-pass radix select (8 bits per pass, shared-memory histogram) finds the value of
-// the budget-th largest score, one ordered compaction pass emits the selected key indices already sorted, and the
-// CTA then copies the selected rows with 16-byte accesses.  Ties at the threshold value are resolved towards the
-// lower key index (torch.topk leaves that choice unspecified).  HBM-bound: reads the scores five times from L2
-// (16 KB per head) and moves 2 * budget * D elements.
+// One to eight CTAs per (batch, head), each of which repeats the (cheap) selection and gathers its share of the
+// rows: the order keys are staged in shared memory once, a 4-pass radix select (8 bits per pass, shared-memory
+// histogram) finds the value of the budget-th largest score, one ordered compaction pass emits the selected key
+// indices already sorted, and the rows are copied with 16-byte accesses.  Ties at the threshold value are
+// resolved towards the lower key index (torch.topk leaves that choice unspecified).  The selection is a chain of
+// block-wide steps on 16 KB of keys (latency-bound); the gather moves 2 * budget * D elements per head.
 #pragma once
 
 #include "common.cuh"
