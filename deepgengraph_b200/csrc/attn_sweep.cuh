@@ -2,8 +2,9 @@
 //
 // The per-key statistics need the FINAL softmax normaliser of every query row, so they are a
 // second sweep over the logits after the forward kernel has produced the base-2 log-sum-exp of
-// each row.  The sweep keeps one 128-row tile stationary in shared memory and streams blocks
-// of the other operand through a TMA ring; the tile product lands in TMEM (double buffered)
+// each row.  The sweep keeps one 128-row tile stationary (in shared memory for 128-wide streamed
+// blocks, in TMEM as the A operand for 64-wide ones) and streams blocks of the other operand
+// through a TMA ring; the tile product lands in TMEM (double buffered)
 // with the STATIONARY rows on the TMEM lanes, so that every thread of the compute warpgroup
 // owns one stationary row and reduces along the streamed dimension in registers:
 //
