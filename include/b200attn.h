@@ -117,7 +117,8 @@ int b200_rotary_embedding_online(const int32_t* positions, void* query, void* ke
  * The kernel is a persistent grid whose CTAs draw query tiles from a counter; every launch takes a counter pair
  * from a pool of 256 per GPU inside the library (returned to zero by the launch itself).  Launches in flight at
  * the same time therefore use different pairs unless more than 256 are outstanding; a launch captured into a
- * CUDA graph keeps the pair it drew at capture time.
+ * CUDA graph keeps the pair it drew at capture time.  The first call on a device looks up the pool's address
+ * (cudaGetSymbolAddress) and sets the kernel's shared-memory attribute: make it before any stream capture.
  */
 int b200_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
                   int batch, int q_len, int kv_len, int heads, int kv_heads, int head_dim,

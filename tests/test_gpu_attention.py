@@ -261,6 +261,30 @@ def test_rescale_path_in_ctas_that_walk_several_tiles(cuda_device):
   torch.testing.assert_close(out.float().cpu(), ref, **TOL)
 
 
+def test_cuda_graph_replay_of_the_persistent_kernel(cuda_device):
+  # a captured launch keeps the tile-counter pair it drew at capture time; the last CTA of every replay must
+  # return it to zero for the next replay
+  q, k, v = (t.to(cuda_device) for t in _qkv(2, 1536, 1536, 12, 4, 128, torch.bfloat16, seed=81))
+  want = att.attn_fwd(q, k, v, window=700)
+  torch.cuda.synchronize()
+  stream = torch.cuda.Stream(device=cuda_device)
+  stream.wait_stream(torch.cuda.current_stream(cuda_device))
+  with torch.cuda.stream(stream):
+    att.attn_fwd(q, k, v, window=700)          # warm-up on the capture stream
+  torch.cuda.current_stream(cuda_device).wait_stream(stream)
+  graph = torch.cuda.CUDAGraph()
+  with torch.cuda.graph(graph):
+    outs = [att.attn_fwd(q, k, v, window=700) for _ in range(3)]
+  for _ in range(4):
+    for o in outs:
+      o.fill_(float("nan"))
+    graph.replay()
+    torch.cuda.synchronize()
+    for o in outs:
+      assert torch.equal(o, want)
+  assert torch.equal(att.attn_fwd(q, k, v, window=700), want)     # eager launches still fine afterwards
+
+
 def test_host_validation(cuda_device):
   q, k, v = (t.to(cuda_device) for t in _qkv(1, 128, 128, 2, 2, 128, torch.bfloat16))
   with pytest.raises(TypeError):
