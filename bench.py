@@ -8,11 +8,20 @@ weak scaling, no data-path collective).
 
 Prints ONE JSON line (rank 0).  `value` is the whole-job TFLOP/s with inputs resident in HBM, timed with
 CUDA events on the launching stream, max over ranks; `e2e` is the same metric through the public operator
-call with HOST (pinned) inputs and the result copied back, copies inside the timed region; `roofline`
-relates the kernel to the measured dense bf16 tensor peak; `cpu_baseline` is the CPU oracle (a port of the
-reference's PyTorch module, fp32) timed on a bounded sample of the same workload.
+call with HOST (pinned) inputs and the result copied back, copies inside the timed region, next to the time
+of the same copies without the kernel (the limit the host link sets); `roofline` relates the kernel to the
+measured dense bf16 tensor peak; `cpu_baseline` is the CPU oracle (a port of the reference's PyTorch module,
+fp32) timed on a bounded sample of the same workload.
 
---impl reference times that CPU port alone (all host threads) and prints the same line shape.
+Further records on the same line:
+  strong_scaling   the FIXED config 2 (128 (batch, head) units) cut into 128 / N units per rank
+  multi_gpu_check  (N > 1) sharded score run + NCCL gather of the score vectors == the one-GPU result, bit for bit
+  sub              (N = 1) one record per other configuration: config 3 (H2O, RoCo), config 4 (KeyFormer), config 5
+                   (attention, whole layer), the reference's Llama-shaped H2O layer, the five bandwidth ops, the
+                   reference's default shape (batch 1, 32 heads, seq 4096, fp16) and the seq-length sweep:
+                   median and min over --sub-iters launches, each timed alone with CUDA events after an L2 flush
+
+--impl reference times the CPU port alone (all host threads) and prints the same line shape.
 FLOPs follow the reference's own formula 4*B*H*S*S*D/2 (run_kernel.py:24).
 """
 import argparse
@@ -32,9 +41,9 @@ sys.path.insert(0, ROOT)
 B, H, S, D = 4, 32, 4096, 128
 METRIC = "causal attn bf16 seq4k d128 TFLOP/s"
 WORKLOAD = "config2: causal MHA bf16, batch 4, 32 heads, seq 4096, head_dim 128 (per GPU)"
-# dram__bytes_read.sum + dram__bytes_write.sum per attn_fwd_kernel launch: ncu capture of the same kernel on 16 of
-# the 128 (batch, head) units (51.7 MB, profiles/attn_fwd_kernel_b1_h16_s4096.md) scaled by 8 -- traffic grows in
-# proportion to the units, every unit reads its q, k, v once from DRAM.
+# dram__bytes_read.sum + dram__bytes_write.sum per attn_fwd_persist_kernel launch: one ncu capture of the same kernel
+# on 16 of the 128 (batch, head) units (53.0 MB) scaled by 8 -- traffic grows in proportion to the units, every unit
+# reads its q, k, v once from DRAM.  A profiler figure carried as a constant: it cannot be measured in a timed run.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 8 * 53.0e6
 
 
@@ -42,14 +51,22 @@ def causal_flops(batch, heads, s, d):
   return 4.0 * batch * heads * s * s * d / 2.0
 
 
+def window_flops(heads, s, d, window):
+  """Visible (query, key) pairs under a causal sliding window, times 4 * d flops per pair and head."""
+  w = min(window, s)
+  pairs = w * (w + 1) / 2.0 + (s - w) * w
+  return 4.0 * d * pairs * heads
+
+
 def load_peaks():
   path = os.path.join(ROOT, "MEASURED_PEAKS.json")
   try:
     with open(path) as f:
       p = json.load(f)
-    return float(p["bf16_tflops"]), float(p.get("bf16_tflops_sustained", 0.0)), "measured"
+    return {"tflops": float(p["bf16_tflops"]), "tflops_sustained": float(p.get("bf16_tflops_sustained", 0.0)),
+            "hbm_gbs": float(p["hbm_gbs"]), "source": "measured"}
   except Exception:
-    return 1590.0, 1400.0, "fallback"
+    return {"tflops": 1590.0, "tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
 
 
 class ClockSampler:
@@ -118,6 +135,9 @@ class ClockSampler:
             "samples": len(s)}
 
 
+# ----------------------------------------------------------------------------------------------------------
+# CPU legs (the oracle port of the reference's PyTorch module; nothing else in this file touches oracle/)
+# ----------------------------------------------------------------------------------------------------------
 def cpu_reference_sample(budget_s, threads=None):
   """Times the CPU oracle (fp32 port of the reference's Attn.forward) on whole heads of the workload, as many
   as fit in `budget_s`.  Returns (tflops, cores, description)."""
@@ -143,6 +163,25 @@ def cpu_reference_sample(budget_s, threads=None):
       break
   return (causal_flops(1, heads, S, D) * passes / dt / 1e12, cores,
           f"{passes} pass(es) over {heads} of {B * H} (batch, head) units of config2, fp32, {dt:.1f} s")
+
+
+def cpu_config1_whole(reps=3):
+  """BASELINE config 1 timed whole on the host cores: causal MHA fp32, batch 1, 32 heads, seq 1024, head_dim 128,
+  q, k, v ~ N(0, 1) / sqrt(128) -- the reference's own CPU-runnable case.  Median of `reps` after one warm-up."""
+  from oracle import reference_math as rm
+  b1, h1, s1, d1 = 1, 32, 1024, 128
+  g = torch.Generator().manual_seed(0)
+  q, k, v = (torch.randn(b1, s1, h1, d1, generator=g) / math.sqrt(d1) for _ in range(3))
+  rm.attention_ref(q, k, v, causal=True, head_chunk=8)
+  ts = []
+  for _ in range(reps):
+    t0 = time.perf_counter()
+    rm.attention_ref(q, k, v, causal=True, head_chunk=8)
+    ts.append(time.perf_counter() - t0)
+  med = sorted(ts)[len(ts) // 2]
+  return {"name": "config1_cpu_whole", "workload": "config1: causal MHA fp32 on CPU, batch 1, 32 heads, seq 1024, head_dim 128",
+          "ms_median": med * 1e3, "ms_min": min(ts) * 1e3, "tflops": causal_flops(b1, h1, s1, d1) / med / 1e12,
+          "cores": torch.get_num_threads(), "kind": "port"}
 
 
 def run_reference_arm(args, rank, world):
@@ -189,14 +228,166 @@ def run_reference_arm(args, rank, world):
   }), flush=True)
 
 
+# ----------------------------------------------------------------------------------------------------------
+# GPU helpers
+# ----------------------------------------------------------------------------------------------------------
+def time_op(fn, iters, warmup, flush=None):
+  """Median and minimum time (microseconds) of `fn()` over `iters` launches, each bracketed by its own pair of CUDA
+  events on the current stream; `flush` (a buffer larger than L2) is rewritten before every timed launch, outside
+  the event pair."""
+  for _ in range(warmup):
+    fn()
+  pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+  for e0, e1 in pairs:
+    if flush is not None:
+      flush.add_(1)
+    e0.record()
+    fn()
+    e1.record()
+  torch.cuda.synchronize()
+  ts = sorted(e0.elapsed_time(e1) * 1e3 for e0, e1 in pairs)
+  return ts[len(ts) // 2], ts[0]
+
+
+def sub_records(dev, peaks, iters, warmup):
+  """One record per configuration other than the headline one (N = 1 only): see the module docstring."""
+  from deepgengraph_b200 import attention as att
+  from deepgengraph_b200 import layer as L
+  from deepgengraph_b200 import native_ops as ops
+  recs = []
+  flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)   # 256 MiB > the 126 MB L2
+  gen = torch.Generator(device=dev).manual_seed(7)
+  peak_tf, peak_bw = peaks["tflops"], peaks["hbm_gbs"]
+
+  def randn(*shape, dtype=torch.bfloat16, scale=1.0):
+    return (torch.randn(*shape, generator=gen, device=dev, dtype=torch.float32) * scale).to(dtype)
+
+  def tensor_rec(name, workload, fn, flops, extra=None):
+    med, mn = time_op(fn, iters, warmup, flush)
+    r = {"name": name, "workload": workload, "us_median": med, "us_min": mn, "tflops": flops / med / 1e6,
+         "bound": "tensor", "frac_of_measured_peak": flops / med / 1e6 / peak_tf, "iters": iters}
+    if extra:
+      r.update(extra)
+    recs.append(r)
+    return r
+
+  def hbm_rec(name, workload, fn, nbytes, extra=None):
+    med, mn = time_op(fn, iters, warmup, flush)
+    r = {"name": name, "workload": workload, "us_median": med, "us_min": mn, "gbs": nbytes / med / 1e3,
+         "bound": "hbm", "algorithmic_bytes": nbytes, "frac_of_measured_peak": nbytes / med / 1e3 / peak_bw,
+         "iters": iters}
+    if extra:
+      r.update(extra)
+    recs.append(r)
+    return r
+
+  # ---- config 3: H2O / RoCo (attention + per-key column sums) ----
+  b3, h3, s3 = 2, 32, 4096
+  q, k, v = (randn(b3, s3, h3, D) for _ in range(3))
+  f3 = causal_flops(b3, h3, s3, D)
+  w3 = "config3: B2 H32 S4096 D128 bf16 causal"
+  tensor_rec("config3_h2o", w3 + ", out + sum_i p", lambda: att.attn_score_fwd(q, k, v), f3,
+             {"credited_flops": "attention only (the second QK^T of the sweep is overhead)"})
+  tensor_rec("config3_roco", w3 + ", out + sum_i p + sum_i p^2", lambda: att.attn_score_fwd(q, k, v, want_sq=True), f3)
+  tensor_rec("config3_forward_only", w3 + ", out only", lambda: att.attn_fwd(q, k, v), f3)
+  score = att.attn_score_fwd(q, k, v)[1]
+  hbm_rec("config3_kv_evict_topk", w3 + ", budget 512: topk -> sort -> gather",
+          lambda: att.kv_evict_topk(score, k, v, 512), score.numel() * 4 + 4 * b3 * 512 * h3 * D * 2)
+  # the reference's default shape (run_kernel.py:20-24; the workload of its Fig. 14): batch 1, 32 heads, seq 4096, fp16
+  qh, kh, vh = (t[:1].to(torch.float16).contiguous() for t in (q, k, v))
+  tensor_rec("reference_default_attn_fp16", "B1 H32 S4096 D128 fp16 causal (run_kernel.py defaults)",
+             lambda: att.attn_fwd(qh, kh, vh), causal_flops(1, 32, 4096, D),
+             {"published_a100_ms": {"FlashTensor": 0.929, "FlashAttention-2": 0.980, "TensorRT": 2.01}})
+  tensor_rec("reference_default_gemma2_fp16", "B1 H32 S4096 D128 fp16 causal, soft-cap 50",
+             lambda: att.attn_fwd(qh, kh, vh, softcap=50.0), causal_flops(1, 32, 4096, D),
+             {"published_a100_ms": {"FlashTensor": 0.937, "FlashAttention-2": 1.314, "TensorRT": 4.27}})
+  tensor_rec("config2_softcap50", "config2 shape (B2 of it) with soft-cap 50", lambda: att.attn_fwd(q, k, v, softcap=50.0), f3)
+  del qh, kh, vh, score
+
+  # ---- seq-length sweep at batch 1, 32 heads (the reference's fig13/run.sh:30) ----
+  for s in (1024, 2048, 4096, 8192):
+    qs, ks, vs = (randn(1, s, 32, D) for _ in range(3))
+    tensor_rec(f"sweep_attn_s{s}", f"B1 H32 S{s} D128 bf16 causal", lambda: att.attn_fwd(qs, ks, vs),
+               causal_flops(1, 32, s, D))
+    tensor_rec(f"sweep_h2o_s{s}", f"B1 H32 S{s} D128 bf16 causal, out + sum_i p", lambda: att.attn_score_fwd(qs, ks, vs),
+               causal_flops(1, 32, s, D))
+  del qs, ks, vs, q, k, v
+
+  # ---- config 4: KeyFormer with the [B, H, S, S] fp32 noise tensor as an input (HBM-bound) ----
+  b4, h4, s4 = 2, 32, 2048
+  q, k, v = (randn(b4, s4, h4, D) for _ in range(3))
+  exp_rand = -torch.log(torch.rand(b4, h4, s4, s4, generator=gen, device=dev).clamp_min_(1e-7))
+  bytes4 = exp_rand.numel() * 4 + 4 * q.numel() * 2 + b4 * h4 * s4 * 4
+  hbm_rec("config4_keyformer", "config4: B2 H32 S2048 D128 bf16 causal, tau 1.0, Gumbel noise tensor input (1.07 GB)",
+          lambda: att.attn_kf_fwd(q, k, v, exp_rand, tau=1.0), bytes4,
+          {"tflops_credited": causal_flops(b4, h4, s4, D) / 1e12, "note": "noise counted once in the algorithmic bytes"})
+  del exp_rand, q, k, v
+
+  # ---- config 5: attention, whole Gemma-2-style layer, bandwidth ops ----
+  cfg = L.Gemma2LayerConfig()
+  s5, T = 8192, 8192
+  q = randn(1, s5, cfg.heads, cfg.head_dim, scale=2.0)
+  k, v = (randn(1, s5, cfg.kv_heads, cfg.head_dim) for _ in range(2))
+  f5 = window_flops(cfg.heads, s5, cfg.head_dim, cfg.window)
+  tensor_rec("config5_attention", "config5: B1 S8192 16q/8kv heads D256 window 4096 soft-cap 50 bf16",
+             lambda: att.attn_fwd(q, k, v, window=cfg.window, softcap=cfg.softcap), f5)
+  del q, k, v
+  w = L.init_weights(cfg, torch.bfloat16, dev, seed=0)
+  x = randn(1, s5, cfg.hidden)
+  qkv_out = (cfg.heads + 2 * cfg.kv_heads) * cfg.head_dim
+  gemm_flops = 2.0 * T * (cfg.hidden * qkv_out + cfg.heads * cfg.head_dim * cfg.hidden +
+                          cfg.hidden * 2 * cfg.intermediate + cfg.intermediate * cfg.hidden)
+  tensor_rec("config5_layer", "config5: Gemma-2-style decoder layer, hidden 3584, GeGLU 14336 (4 cuBLAS GEMMs + this library's ops)",
+             lambda: L.gemma2_layer(x, w, cfg), gemm_flops + f5, {"gemm_tflop": gemm_flops / 1e12})
+  del w
+  sz = 2
+  hid = cfg.hidden
+  xin, out = randn(T, hid), torch.empty(T, hid, dtype=torch.bfloat16, device=dev)
+  wn = (1 + 0.02 * randn(hid).float()).to(torch.bfloat16)
+  hbm_rec("rms_norm", f"[{T}, {hid}] bf16", lambda: ops.rms_norm(out, xin, wn, cfg.eps), 2 * T * hid * sz + hid * sz)
+  res = randn(T, hid)
+  hbm_rec("fused_add_rms_norm", f"[{T}, {hid}] bf16, in place", lambda: ops.fused_add_rms_norm(xin, res, wn, cfg.eps),
+          4 * T * hid * sz)
+  del xin, out, res
+  gu = randn(T, 2 * cfg.intermediate)
+  act = torch.empty(T, cfg.intermediate, dtype=torch.bfloat16, device=dev)
+  hbm_rec("gelu_tanh_and_mul", f"[{T}, 2x{cfg.intermediate}] bf16", lambda: ops.gelu_tanh_and_mul(act, gu),
+          3 * T * cfg.intermediate * sz)
+  hbm_rec("silu_and_mul", f"[{T}, 2x{cfg.intermediate}] bf16", lambda: ops.silu_and_mul(act, gu),
+          3 * T * cfg.intermediate * sz)
+  del gu, act
+  qr, kr = randn(T, cfg.heads * cfg.head_dim), randn(T, cfg.kv_heads * cfg.head_dim)
+  pos = torch.arange(T, dtype=torch.int32, device=dev)
+  hbm_rec("rotary_embedding_online", f"q [{T}, {cfg.heads}x{cfg.head_dim}], k [{T}, {cfg.kv_heads}x{cfg.head_dim}] bf16",
+          lambda: ops.rotary_embedding_online(pos, qr, kr, cfg.head_dim, cfg.rope_theta),
+          2 * T * (cfg.heads + cfg.kv_heads) * cfg.head_dim * sz + 4 * T)
+  del qr, kr
+
+  # ---- the reference's Llama-shaped layer with a score variant and the eviction fused in (models/h2o.py:34-86),
+  #      random weights as in run_e2e.py:48-66: hidden 4096, 32 heads, intermediate 11008, fp16, seq 4096 ----
+  lc = L.LlamaLayerConfig()
+  lw = L.init_llama_weights(lc, torch.float16, dev, seed=0)
+  sl = 4096
+  xl = randn(1, sl, lc.hidden, dtype=torch.float16)
+  lg = 2.0 * sl * (lc.hidden * 3 * lc.hidden + lc.hidden * lc.hidden + lc.hidden * 2 * lc.intermediate +
+                   lc.intermediate * lc.hidden)
+  for variant in ("h2o", "roco"):
+    tensor_rec(f"llama_layer_{variant}", f"Llama-7B-shaped layer fp16, seq 4096, {variant} scores + KV eviction to 512 keys",
+               lambda: L.llama_score_layer(xl, lw, lc, variant), lg + causal_flops(1, lc.heads, sl, lc.head_dim),
+               {"gemm_tflop": lg / 1e12})
+  return recs
+
+
 def main():
   ap = argparse.ArgumentParser()
   ap.add_argument("--gpus", type=int, default=1)
   ap.add_argument("--steps", type=int, default=100)
   ap.add_argument("--warmup", type=int, default=10)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-  ap.add_argument("--e2e-steps", type=int, default=20)
+  ap.add_argument("--e2e-steps", type=int, default=50)
+  ap.add_argument("--sub-iters", type=int, default=100)
   ap.add_argument("--no-cpu-baseline", action="store_true")
+  ap.add_argument("--no-sub", action="store_true", help="skip the per-configuration sub-records (N = 1)")
   args = ap.parse_args()
   args.warmup = max(args.warmup, 3)
 
@@ -210,6 +401,7 @@ def main():
 
   import torch.distributed as dist
   from deepgengraph_b200 import attention as att
+  from deepgengraph_b200 import sharding as sh
 
   torch.cuda.set_device(local_rank)
   dev = torch.device("cuda", local_rank)
@@ -221,6 +413,12 @@ def main():
     if world > 1:
       dist.barrier()
     torch.cuda.synchronize()
+
+  def max_over_ranks(x):
+    t = torch.tensor([x], dtype=torch.float64, device=dev)
+    if world > 1:
+      dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
 
   # this rank's shard: B x H (batch, head) units, generated locally from seed + rank (no scatter is timed)
   gen = torch.Generator(device=dev).manual_seed(1234 + rank)
@@ -236,27 +434,52 @@ def main():
   sampler.start()
 
   # ---- device-resident timing: K steps, CUDA events on the launching (current) stream ----
-  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
   barrier()
-  e0.record()
-  for _ in range(args.steps):
+  evs[0].record()
+  for i in range(args.steps):
     out = att.attn_fwd(q, k, v, causal=True)
-  e1.record()
+    evs[i + 1].record()
   barrier()
-  ms_total = e0.elapsed_time(e1)
-  t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
-  if world > 1:
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-  ms_step = t.item() / args.steps
+  ms_step = max_over_ranks(evs[0].elapsed_time(evs[-1])) / args.steps
   value = world * flops_rank / (ms_step * 1e-3) / 1e12
+  per_step = sorted(evs[i].elapsed_time(evs[i + 1]) * 1e3 for i in range(args.steps))   # this rank, microseconds
+
+  # ---- strong scaling: the FIXED config 2 (B x H = 128 units) cut into 128 / world units per rank ----
+  lo, hi = sh.unit_range(B * H, world, rank)
+  units = hi - lo
+  if units % H == 0:
+    shape = (units // H, S, H, D)          # whole batch elements
+  else:
+    shape = (1, S, units, D)               # part of one batch element's heads
+  if world == 1:
+    ms_strong = ms_step
+  else:
+    qs, ks, vs = (t.reshape(-1)[:shape[0] * S * shape[2] * D].view(shape) for t in (q, k, v))
+    for _ in range(args.warmup):
+      att.attn_fwd(qs, ks, vs, causal=True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+      att.attn_fwd(qs, ks, vs, causal=True)
+    e1.record()
+    barrier()
+    ms_strong = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    del qs, ks, vs
+  strong = {"workload": "config2 as ONE fixed problem (128 (batch, head) units), cut into equal unit ranges",
+            "units_per_rank": units, "ms_per_step": ms_strong, "value": flops_rank / (ms_strong * 1e-3) / 1e12,
+            "unit": "TFLOP/s", "scaling": "strong"}
 
   # ---- end to end: pinned host inputs -> H2D -> kernel -> D2H of the result, every step ----
   # Every step copies its own q, k, v from pinned host memory and copies its output back.  Copies and kernels run
   # on three streams with two device buffer sets, so that step i+1's upload and step i-1's download overlap step
-  # i's kernel (the operator call itself is the public attention.attn_fwd on the current stream).
+  # i's kernel (the operator call itself is the public attention.attn_fwd on the current stream).  The same
+  # schedule without the kernel ("copy only") is timed next to it: that is the limit the host link sets.
   qh, kh, vh = (x.cpu().pin_memory() for x in (q, k, v))
   oh = [torch.empty_like(qh).pin_memory() for _ in range(2)]
   dev_in = [tuple(torch.empty_like(t) for t in (q, k, v)) for _ in range(2)]
+  dev_out = [torch.empty_like(q) for _ in range(2)]
   s_h2d, s_run, s_d2h = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
   ev_in = [torch.cuda.Event() for _ in range(2)]      # upload of buffer set b finished
   ev_free = [torch.cuda.Event() for _ in range(2)]    # kernel that read buffer set b finished
@@ -264,7 +487,7 @@ def main():
   ev_done = [torch.cuda.Event() for _ in range(2)]    # download of slot b finished
   outs = [None, None]
 
-  def e2e_step(i):
+  def e2e_step(i, with_kernel):
     b = i & 1
     with torch.cuda.stream(s_h2d):
       s_h2d.wait_event(ev_free[b])
@@ -274,7 +497,7 @@ def main():
     with torch.cuda.stream(s_run):
       s_run.wait_event(ev_in[b])
       s_run.wait_event(ev_done[b])                     # the previous output in this slot has left the device
-      outs[b] = att.attn_fwd(*dev_in[b], causal=True)
+      outs[b] = att.attn_fwd(*dev_in[b], causal=True) if with_kernel else dev_out[b]
       ev_free[b].record(s_run)
       ev_out[b].record(s_run)
     with torch.cuda.stream(s_d2h):
@@ -282,26 +505,46 @@ def main():
       oh[b].copy_(outs[b], non_blocking=True)
       ev_done[b].record(s_d2h)
 
-  def e2e_run(n):
+  def e2e_run(n, with_kernel):
     for i in range(n):
-      e2e_step(i)
+      e2e_step(i, with_kernel)
     for st in (s_h2d, s_run, s_d2h):
       torch.cuda.current_stream(dev).wait_stream(st)
 
-  e2e_run(4)
-  barrier()
-  e0.record()
-  e2e_run(args.e2e_steps)
-  e1.record()
-  barrier()
-  t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-  if world > 1:
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-  e2e_ms = t.item() / args.e2e_steps
+  def e2e_timed(with_kernel):
+    e2e_run(4, with_kernel)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    e2e_run(args.e2e_steps, with_kernel)
+    e1.record()
+    barrier()
+    return max_over_ranks(e0.elapsed_time(e1)) / args.e2e_steps
+
+  e2e_ms = e2e_timed(True)
   e2e_value = world * flops_rank / (e2e_ms * 1e-3) / 1e12
   if not torch.equal(oh[(args.e2e_steps - 1) & 1], out.cpu()):
     raise RuntimeError("end-to-end output differs from the device-resident run")
-  clocks = sampler.stop()
+  clocks = sampler.stop()          # the copy-only leg below leaves the SMs idle: not part of the clock record
+  copy_ms = e2e_timed(False)
+  del qh, kh, vh, oh, dev_in, dev_out, outs
+
+  # ---- multi-GPU correctness: sharded score run + NCCL gather == the one-GPU run, bit for bit ----
+  multi_check = None
+  if world > 1:
+    bc, hc, sc = 2, 32, 4096                                        # config 3's shape; the same problem on every rank
+    g3 = torch.Generator(device=dev).manual_seed(99)
+    q3, k3, v3 = (torch.randn(bc, sc, hc, D, generator=g3, device=dev, dtype=torch.bfloat16) for _ in range(3))
+    results = sh.run_sharded(lambda a, b_, c: att.attn_score_fwd(a, b_, c), q3, k3, v3, world, rank)
+    full = sh.gather_scores(sh.scores_from_pieces(results, index=1), bc * hc, world, rank)
+    ref_out, ref_score = att.attn_score_fwd(q3, k3, v3)
+    ok = torch.equal(full, ref_score.reshape(bc * hc, sc))
+    for piece, (o, _) in results:
+      ok = ok and torch.equal(o[0], ref_out[piece.b, :, piece.hk_lo:piece.hk_hi])
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    multi_check = "ok" if flag.item() == 1 else "MISMATCH"
+    del q3, k3, v3, results, full, ref_out, ref_score
 
   # no bounded device-side wait may have expired
   import ctypes
@@ -312,9 +555,12 @@ def main():
     raise RuntimeError(f"device status word {word.value:#x}: a kernel wait expired, the numbers are void")
   if not torch.isfinite(out.float()).all():
     raise RuntimeError("non-finite attention output")
+  if multi_check == "MISMATCH":
+    raise RuntimeError("sharded run differs from the single-GPU run")
 
   if rank == 0:
-    peak_burst, peak_sustained, peak_src = load_peaks()
+    peaks = load_peaks()
+    peak_burst = peaks["tflops"]
     achieved = flops_rank / (ms_step * 1e-3) / 1e12   # per GPU, per launch: one kernel per step
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
@@ -323,19 +569,30 @@ def main():
         "config": {"workload": WORKLOAD, "global_batch": B * world, "heads": H, "seq_len": S, "head_dim": D,
                    "parallelism": f"batch x head sharded over {world} GPU(s), no collective",
                    "l2": "q,k,v,out = 537 MB per GPU, larger than the 126 MB L2",
-                   "us_per_core_module": ms_step * 1e3, "e2e_steps": args.e2e_steps},
+                   "us_per_core_module": ms_step * 1e3, "us_median": per_step[len(per_step) // 2],
+                   "us_min": per_step[0], "e2e_steps": args.e2e_steps},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_burst, "unit": "TFLOP/s",
                      "frac": achieved / peak_burst, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-                     "peak_source": f"{peak_src} (cuBLAS bf16 burst; sustained {peak_sustained})",
+                     "traffic_source": "ncu dram__bytes of a 16-unit capture x 8 (constant, not measured in this run)",
+                     "peak_source": f"{peaks['source']} (cuBLAS bf16 burst; sustained {peaks['tflops_sustained']})",
                      "frac_of_datasheet_2250": achieved / 2250.0},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": 3 * q.numel() * 2,
-                "d2h_bytes_per_step": q.numel() * 2, "ms_per_step": e2e_ms},
+                "d2h_bytes_per_step": q.numel() * 2, "ms_per_step": e2e_ms, "copy_only_ms_per_step": copy_ms,
+                "frac_of_copy_limit": copy_ms / e2e_ms},
+        "strong_scaling": strong,
         "gpu_launches": args.steps,
         "clocks": clocks,
     }
+    if multi_check is not None:
+      line["multi_gpu_check"] = multi_check
+    del q, k, v, out
+    torch.cuda.empty_cache()
+    if world == 1 and not args.no_sub:
+      line["sub"] = sub_records(dev, peaks, args.sub_iters, 20)
     if world == 1 and not args.no_cpu_baseline:
       tf, cores, sample = cpu_reference_sample(budget_s=15.0)
       line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample}
+      line.setdefault("sub", []).append(cpu_config1_whole())
     print(json.dumps(line), flush=True)
 
   if world > 1:

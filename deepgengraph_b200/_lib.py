@@ -37,7 +37,9 @@ SIGNATURES = {
                                    _i, _i, _f, _f, _vp]),
     "b200_attn_score_workspace_bytes": (_i64, [_i, _i, _i, _i]),
     "b200_attn_score": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]),
-    "b200_attn_score_gqa": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]),
+    "b200_attn_score_gqa": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f,
+                                 _vp]),
+    "b200_attn_kf_score_gqa": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]),
     "b200_attn_score_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]),
     "b200_attn_corm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "b200_avg_pool1d_f32": (_i, [_vp, _vp, _i64, _i, _i, _vp]),
@@ -60,7 +62,7 @@ def load():
   if _build.needs_build():
     try:
       _build.build()
-    except Exception as e:  # stale-but-present library is still usable (e.g. no nvcc on the GPU box)
+    except Exception as e:  # a present library is still usable where no compiler is installed
       if not os.path.exists(path):
         raise RuntimeError(f"libb200attn.so is missing and could not be built: {e}") from e
   lib = ctypes.CDLL(path)

@@ -90,14 +90,11 @@ def _attn_score_impl(q, k, v, want_sq, causal, window, softcap, scale):
   dev = _check_qkv(where, q, k, v)
   B, Sq, H, D = q.shape
   Skv, Hk = k.size(1), k.size(2)
-  if H != Hk and want_sq:
-    raise ValueError(f"{where}: the squared statistic needs heads == kv heads (the group mean does not commute "
-                     "with the square; the reference asserts group_size == 1)")
   if scale is None or scale <= 0:
     scale = 1.0 / math.sqrt(D)
   out = torch.empty_like(q)
   score = torch.empty((B, Hk, Skv), dtype=torch.float32, device=dev)
-  score_sq = torch.empty((B, H, Skv), dtype=torch.float32, device=dev) if want_sq else None
+  score_sq = torch.empty((B, Hk, Skv), dtype=torch.float32, device=dev) if want_sq else None
   if B == 0 or Sq == 0:   # no queries: every column sum is an empty sum
     score.zero_()
     if want_sq:
@@ -105,14 +102,15 @@ def _attn_score_impl(q, k, v, want_sq, causal, window, softcap, scale):
     return (out, score, score_sq) if want_sq else (out, score)
   ws, nbytes = _workspace(dev, B, Sq, Skv, H)
   if H != Hk:
-    # grouped-query attention: mean over the query heads of a K/V head, then the column sum (kernels/roco.py:39-40)
+    # grouped-query attention: mean over the query heads of a K/V head, then the sums (kernels/roco.py:39-46)
     with torch.cuda.device(dev):
       st = _lib.load().b200_attn_score_gqa(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
-                                           score.data_ptr(), ws.data_ptr(), nbytes, B, Sq, Skv, H, Hk, D,
-                                           _dtype_code(q, where), int(bool(causal)), int(window), float(softcap),
-                                           float(scale), _stream_ptr(dev))
+                                           score.data_ptr(), score_sq.data_ptr() if want_sq else None, None,
+                                           ws.data_ptr(), nbytes, B, Sq, Skv, H, Hk, D, _dtype_code(q, where),
+                                           int(bool(causal)), int(window), float(softcap), float(scale),
+                                           _stream_ptr(dev))
     _lib.check(st, where)
-    return out, score
+    return (out, score, score_sq) if want_sq else (out, score)
   with torch.cuda.device(dev):
     st = _lib.load().b200_attn_score(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), score.data_ptr(),
                                      score_sq.data_ptr() if want_sq else None, ws.data_ptr(), nbytes, B, Sq, Skv, H,
@@ -138,18 +136,25 @@ def _attn_corm_impl(q, k, v, causal, scale):
   dev = _check_qkv(where, q, k, v)
   B, Sq, H, D = q.shape
   Skv, Hk = k.size(1), k.size(2)
-  if H != Hk:
-    raise ValueError(f"{where}: needs heads == kv heads (the reference asserts group_size == 1)")
   if scale is None or scale <= 0:
     scale = 1.0 / math.sqrt(D)
   out = torch.empty_like(q)
-  score = torch.empty((B, H, Skv), dtype=torch.float32, device=dev)
-  flags = torch.empty((B, H, Skv), dtype=torch.uint8, device=dev)
+  score = torch.empty((B, Hk, Skv), dtype=torch.float32, device=dev)
+  flags = torch.empty((B, Hk, Skv), dtype=torch.uint8, device=dev)
+  if B == 0 or Sq == 0:   # no queries: `any` over an empty set
+    flags.zero_()
+    return out, flags.view(torch.bool)
   ws, nbytes = _workspace(dev, B, Sq, Skv, H)
   with torch.cuda.device(dev):
-    st = _lib.load().b200_attn_corm(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), score.data_ptr(),
-                                    flags.data_ptr(), ws.data_ptr(), nbytes, B, Sq, Skv, H, D, _dtype_code(q, where),
-                                    int(bool(causal)), float(scale), _stream_ptr(dev))
+    if H != Hk:   # thresholds applied to the group-mean probabilities
+      st = _lib.load().b200_attn_score_gqa(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                           score.data_ptr(), None, flags.data_ptr(), ws.data_ptr(), nbytes, B, Sq,
+                                           Skv, H, Hk, D, _dtype_code(q, where), int(bool(causal)), 0, 0.0,
+                                           float(scale), _stream_ptr(dev))
+    else:
+      st = _lib.load().b200_attn_corm(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), score.data_ptr(),
+                                      flags.data_ptr(), ws.data_ptr(), nbytes, B, Sq, Skv, H, D,
+                                      _dtype_code(q, where), int(bool(causal)), float(scale), _stream_ptr(dev))
   _lib.check(st, where)
   return out, flags.view(torch.bool)
 
@@ -159,21 +164,27 @@ def _attn_kf_impl(q, k, v, exp_rand, tau, causal, scale):
   dev = _check_qkv(where, q, k, v)
   B, Sq, H, D = q.shape
   Skv, Hk = k.size(1), k.size(2)
-  if H != Hk:
-    raise ValueError(f"{where}: needs heads == kv heads (the reference asserts group_size == 1)")
   _require_cuda(where, q, exp_rand)
   if exp_rand.dtype != torch.float32 or tuple(exp_rand.shape) != (B, H, Sq, Skv) or not exp_rand.is_contiguous():
     raise ValueError(f"{where}: exp_rand must be contiguous float32 [batch, heads, q_len, kv_len]")
   if scale is None or scale <= 0:
     scale = 1.0 / math.sqrt(D)
   out = torch.empty_like(q)
-  score = torch.empty((B, H, Skv), dtype=torch.float32, device=dev)
+  score = torch.empty((B, Hk, Skv), dtype=torch.float32, device=dev)
+  if B == 0 or Sq == 0:
+    return out, score.zero_()
   ws, nbytes = _workspace(dev, B, Sq, Skv, H)
   with torch.cuda.device(dev):
-    st = _lib.load().b200_attn_kf_score(q.data_ptr(), k.data_ptr(), v.data_ptr(), exp_rand.data_ptr(),
-                                        out.data_ptr(), score.data_ptr(), ws.data_ptr(), nbytes, B, Sq, Skv, H, D,
-                                        _dtype_code(q, where), int(bool(causal)), float(tau), float(scale),
-                                        _stream_ptr(dev))
+    if H != Hk:   # score of a K/V head = mean over its query heads (figure/membound/attn.py:162-165)
+      st = _lib.load().b200_attn_kf_score_gqa(q.data_ptr(), k.data_ptr(), v.data_ptr(), exp_rand.data_ptr(),
+                                              out.data_ptr(), score.data_ptr(), ws.data_ptr(), nbytes, B, Sq, Skv, H,
+                                              Hk, D, _dtype_code(q, where), int(bool(causal)), float(tau),
+                                              float(scale), _stream_ptr(dev))
+    else:
+      st = _lib.load().b200_attn_kf_score(q.data_ptr(), k.data_ptr(), v.data_ptr(), exp_rand.data_ptr(),
+                                          out.data_ptr(), score.data_ptr(), ws.data_ptr(), nbytes, B, Sq, Skv, H, D,
+                                          _dtype_code(q, where), int(bool(causal)), float(tau), float(scale),
+                                          _stream_ptr(dev))
   _lib.check(st, where)
   return out, score
 

@@ -53,7 +53,10 @@ def compile(model, input_names, inputs, output_names, system=SYSTEM):
     def f(q, k, v):
       return _att.attn_snapkv_fwd(q, k, v, kernel_size=ks, causal=True)
   elif name == 'Corm':
+    from .kernels import check_corm_mask
+
     def f(q, k, v, corm_mask=None):
+      check_corm_mask(corm_mask, q.shape[1], k.shape[1])   # only the thresholds of Corm.prepare are implemented
       return _att.attn_corm_fwd(q, k, v, causal=True)
   else:
     tau = float(model.tau)

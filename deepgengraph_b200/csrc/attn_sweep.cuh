@@ -33,6 +33,13 @@ enum SweepMode : int { SWEEP_COLSUM = 0, SWEEP_KF_COLSUM = 1, SWEEP_KF_ROWLSE = 
 // second per-key statistic of the column-sum sweep: none, sum of p^2 (RoCo), or the Corm flag
 enum SweepAux : int { AUX_NONE = 0, AUX_SQUARES = 1, AUX_CORM = 2 };
 
+// Of every 8 groups of 4 columns of an unmasked block, this many take their exponentials from the FMA-pipe
+// polynomial instead of the special-function unit (column-sum sweeps).
+#ifndef B200_SWEEP_POLY_OF_8
+#define B200_SWEEP_POLY_OF_8 0
+#endif
+constexpr int kSweepPolyOf8 = B200_SWEEP_POLY_OF_8;
+
 struct SweepParams {
   const float* lse;     // [B*H][lse_stride]  row normalisers (COLSUM: L, KF_COLSUM: Lz)
   float* lse_out;       // [B*H][lse_stride]  KF_ROWLSE output
@@ -93,10 +100,14 @@ struct SweepCtx {
 };
 
 // ------------------------------- TMA producer -------------------------------
-template <class Cfg>
+// GROUPED (column sums of the group-mean probabilities): the CTA belongs to one K/V head and streams, for every
+// query block, the blocks of the `kv_group` query heads that share it, one after the other (item n = block
+// n / kv_group of query head c.h * kv_group + n % kv_group).
+template <class Cfg, bool GROUPED>
 __device__ __forceinline__ void sweep_producer(const SweepCtx<Cfg>& c, const SweepParams& p, const CUtensorMap* tm_a,
                                                const CUtensorMap* tm_x, const CUtensorMap* tm_n) {
   constexpr int ST = Cfg::STAGES, BX = Cfg::BX;
+  static_assert(!GROUPED || (Cfg::A_TMEM && !Cfg::NOISE), "grouped sweep: stationary tile in TMEM, no noise");
   if constexpr (!Cfg::A_TMEM) {
     mbar_expect_tx(&c.bars[Cfg::BAR_A_FULL], Cfg::A_BYTES);
 #pragma unroll
@@ -106,8 +117,15 @@ __device__ __forceinline__ void sweep_producer(const SweepCtx<Cfg>& c, const Swe
   }
   bool ok = true;
   int n_issued = 0;
-  for (int blk = c.blk_lo; blk < c.blk_hi; ++blk) {
-    const int n = blk - c.blk_lo, st = n % ST, use = n / ST;
+  const int group = GROUPED ? p.kv_group : 1;
+  const int n_items = (c.blk_hi - c.blk_lo) * group;
+  for (int n = 0; n < n_items; ++n) {
+    const int blk = c.blk_lo + (GROUPED ? n / group : n);
+    const int st = n % ST, use = n / ST;
+    // head of the streamed operand, and the row of the normaliser table that goes with it
+    const int x_head = GROUPED ? c.h * group + (n - (blk - c.blk_lo) * group)
+                               : (Cfg::MODE == SWEEP_KF_ROWLSE ? c.h / p.kv_group : c.h);
+    const int lse_row = GROUPED ? c.b * p.heads + x_head : c.bh;
     if (use > 0 && !mbar_wait(&c.bars[Cfg::BAR_X_EMPTY + st], (use - 1) & 1, c.abort_flag, WAIT_X_EMPTY)) {
       ok = false;
       break;
@@ -116,7 +134,7 @@ __device__ __forceinline__ void sweep_producer(const SweepCtx<Cfg>& c, const Swe
 #pragma unroll
     for (int ks = 0; ks < 2; ++ks)
       tma_load_4d(c.sX + st * Cfg::X_STAGE_BYTES + ks * (BX * 128), tm_x, &c.bars[Cfg::BAR_X_FULL + st], ks * 64,
-                  Cfg::MODE == SWEEP_KF_ROWLSE ? c.h / p.kv_group : c.h, blk * BX, c.b);
+                  x_head, blk * BX, c.b);
     if constexpr (Cfg::N_STAGE_BYTES > 0) {
       if (use > 0 && !mbar_wait(&c.bars[Cfg::BAR_N_EMPTY + st], (use - 1) & 1, c.abort_flag, WAIT_N_EMPTY)) {
         ok = false;
@@ -143,7 +161,7 @@ __device__ __forceinline__ void sweep_producer(const SweepCtx<Cfg>& c, const Swe
       }
       if constexpr (Cfg::LSE_IN) {
         // 1-D bulk copy of the BX row normalisers of this query block (lse rows are padded to 128)
-        const float* src = p.lse + (int64_t)c.bh * p.lse_stride + blk * BX;
+        const float* src = p.lse + (int64_t)lse_row * p.lse_stride + blk * BX;
         asm volatile(
             "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
             ::"r"(smem_u32(dst + Cfg::NOISE_BYTES)), "l"(src), "r"((uint32_t)Cfg::LSE_BYTES),
@@ -175,14 +193,14 @@ __device__ __forceinline__ void sweep_producer(const SweepCtx<Cfg>& c, const Swe
 // All 32 lanes walk the loop (warp-uniform control flow keeps the descriptor arithmetic on the uniform
 // datapath); one elected lane issues.
 template <class Cfg, bool BF16>
-__device__ __forceinline__ void sweep_mma(const SweepCtx<Cfg>& c) {
+__device__ __forceinline__ void sweep_mma(const SweepCtx<Cfg>& c, int n_items) {
   constexpr int ST = Cfg::STAGES, BX = Cfg::BX;
   constexpr uint32_t IDESC = make_idesc(BF16, 128, BX, false, false);
   const uint32_t desc_hi = smem_desc_hi(1024);
   const uint32_t a_lo = smem_desc_lo(smem_u32(c.sA), 16), x_lo = smem_desc_lo(smem_u32(c.sX), 16);
   bool ok = mbar_wait(&c.bars[Cfg::BAR_A_FULL], 0, c.abort_flag, WAIT_Q_FULL);
-  for (int blk = c.blk_lo; blk < c.blk_hi && ok; ++blk) {
-    const int n = blk - c.blk_lo, st = n % ST, tb = n & 1, tuse = n >> 1;
+  for (int n = 0; n < n_items && ok; ++n) {
+    const int st = n % ST, tb = n & 1, tuse = n >> 1;
     if (tuse > 0) ok = mbar_wait(&c.bars[Cfg::BAR_T_EMPTY + tb], (tuse - 1) & 1, c.abort_flag, WAIT_T_EMPTY);
     ok = ok && mbar_wait(&c.bars[Cfg::BAR_X_FULL + st], (n / ST) & 1, c.abort_flag, WAIT_X_FULL);
     if (!ok) break;
@@ -262,7 +280,18 @@ __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, con
         e0 = ffma2(make_float2(sv[0], sv[1]), c2, make_float2(-L.x, -L.y));
         e1 = ffma2(make_float2(sv[2], sv[3]), c2, make_float2(-L.z, -L.w));
       }
-      float pr[4] = {ex2_approx(e0.x), ex2_approx(e0.y), ex2_approx(e1.x), ex2_approx(e1.y)};
+      float pr[4];
+      // A fixed, interleaved subset of the column groups of unmasked blocks takes its exponentials from the cubic
+      // polynomial on the FMA pipe (exp2_poly2, relative error 7.5e-5): the sweep issues one exponential per
+      // element and nothing else of weight, so the special-function unit (16 results per clock per SM) is its
+      // bound; the share is kSweepPolyOf8 / 8.
+      if (!MASK && (((i / 4) * kSweepPolyOf8) % 8) < kSweepPolyOf8) {
+        e0 = exp2_poly2(e0);
+        e1 = exp2_poly2(e1);
+        pr[0] = e0.x, pr[1] = e0.y, pr[2] = e1.x, pr[3] = e1.y;
+      } else {
+        pr[0] = ex2_approx(e0.x), pr[1] = ex2_approx(e0.y), pr[2] = ex2_approx(e1.x), pr[3] = ex2_approx(e1.y);
+      }
       if constexpr (MASK) {
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -331,6 +360,96 @@ __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, con
   if constexpr (AUX == AUX_CORM) p.partial_sq[off] = fmaxf(sq0, sq1);
 }
 
+
+// ------------- compute: per-key sums of the GROUP-MEAN probabilities ----------
+// Grouped-query attention: the statistics are taken from pm_ij = (1 / g) sum_h p^h_ij, the probabilities averaged
+// over the g query heads that share the K/V head (kernels/roco.py:39-40: mean over the group, THEN the square;
+// figure/membound/attn.py:84-88, 240-242).  The g product tiles of one query block arrive one after the other;
+// the thread of key j keeps the running sums over the heads for the block's 64 queries in registers and folds
+// them into its accumulators after the last head of the group.
+template <class Cfg, bool SOFTCAP, int AUX>
+__device__ __forceinline__ void sweep_compute_colsum_grouped(const SweepCtx<Cfg>& c, const SweepParams& p, int chunk) {
+  constexpr int ST = Cfg::STAGES, BX = Cfg::BX;
+  static_assert(BX == 64, "the grouped sweep keeps one 64-query block of running sums in registers");
+  const int warp_q = (threadIdx.x >> 5) & 3, lane = threadIdx.x & 31;
+  const int key = c.a0 + warp_q * 32 + lane;
+  const uint32_t lane_addr = c.tmem_base + ((uint32_t)(warp_q * 32) << 16);
+  const float cmul = SOFTCAP ? 1.0f : p.scale_log2;
+  int i_lo = p.causal ? key - p.delta : 0;
+  int i_hi = (p.causal && p.window > 0) ? min(p.q_len - 1, key + p.window - 1 - p.delta) : p.q_len - 1;
+  if (key >= p.kv_len) {
+    i_lo = 1 << 28;
+    i_hi = -1;
+  }
+  const int group = p.kv_group;
+  const float inv_g = 1.0f / (float)group;
+  const int n_items = (c.blk_hi - c.blk_lo) * group;
+  float acc = 0.f, aux = 0.f;
+  float pbar[BX];
+#pragma unroll
+  for (int i = 0; i < BX; ++i) pbar[i] = 0.f;
+  int blk = c.blk_lo, hh = 0;
+  for (int n = 0; n < n_items; ++n) {
+    const int st = n % ST, tb = n & 1;
+    if (!mbar_wait(&c.bars[Cfg::BAR_T_FULL + tb], (n >> 1) & 1, c.abort_flag, WAIT_T_FULL)) return;
+    if (!mbar_wait(&c.bars[Cfg::BAR_N_FULL + st], (n / ST) & 1, c.abort_flag, WAIT_N_FULL)) return;
+    tc_fence_after();
+    const float* lse_s = reinterpret_cast<const float*>(c.sN + st * Cfg::N_STAGE_STRIDE + Cfg::NOISE_BYTES);
+    const int i0 = blk * BX;
+    const int lo_c = i_lo - i0, hi_c = i_hi - i0;
+    const float keep = hh == 0 ? 0.f : 1.f;   // the first head of a group starts the running sums afresh
+#pragma unroll
+    for (int ch = 0; ch < BX / 32; ++ch) {
+      uint32_t sr[32];
+      tmem_ld32(lane_addr + tb * BX + ch * 32, sr);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        const float4 L = *reinterpret_cast<const float4*>(lse_s + ch * 32 + i);
+        float sv[4] = {__uint_as_float(sr[i]), __uint_as_float(sr[i + 1]), __uint_as_float(sr[i + 2]),
+                       __uint_as_float(sr[i + 3])};
+        if constexpr (SOFTCAP) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) sv[u] = tanh_approx(sv[u] * p.cap_in) * p.cap_out;
+        }
+        const float2 c2 = make_float2(cmul, cmul);
+        const float2 e0 = ffma2(make_float2(sv[0], sv[1]), c2, make_float2(-L.x, -L.y));
+        const float2 e1 = ffma2(make_float2(sv[2], sv[3]), c2, make_float2(-L.z, -L.w));
+        float pr[4] = {ex2_approx(e0.x), ex2_approx(e0.y), ex2_approx(e1.x), ex2_approx(e1.y)};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int col = ch * 32 + i + u;
+          if (col < lo_c || col > hi_c) pr[u] = 0.f;   // masked pair, or a row / column beyond the tensors
+          pbar[col] = fmaf(pbar[col], keep, pr[u]);
+        }
+      }
+    }
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) {
+      mbar_arrive(&c.bars[Cfg::BAR_T_EMPTY + tb]);
+      mbar_arrive(&c.bars[Cfg::BAR_N_EMPTY + st]);
+    }
+    if (hh == group - 1) {
+      const float q1 = (float)(i0 + 1);
+#pragma unroll
+      for (int col = 0; col < BX; ++col) {
+        const float pm = pbar[col] * inv_g;
+        acc += pm;
+        if constexpr (AUX == AUX_SQUARES) aux = fmaf(pm, pm, aux);
+        if constexpr (AUX == AUX_CORM) aux = fmaxf(aux, pm * (q1 + (float)col) >= 1.0f ? 1.0f : 0.0f);
+      }
+      hh = 0;
+      ++blk;
+    } else {
+      ++hh;
+    }
+  }
+  const int64_t off = ((int64_t)c.bh * p.n_chunks + chunk) * p.kv_pad + key;
+  p.partial[off] = acc;
+  if constexpr (AUX != AUX_NONE) p.partial_sq[off] = aux;
+}
+
 // --------------------- compute: per-query log-sum-exp of z --------------------
 template <class Cfg>
 __device__ __forceinline__ void sweep_compute_rowlse(const SweepCtx<Cfg>& c, const SweepParams& p) {
@@ -393,7 +512,11 @@ __device__ __forceinline__ void sweep_compute_rowlse(const SweepCtx<Cfg>& c, con
 }
 
 // ----------------------------------- kernel ----------------------------------
-template <int MODE, int BX, int STAGES, bool BF16, bool SOFTCAP, int AUX>
+// Grid: x = (batch, head) unit -- (batch, K/V head) when GROUPED --, y = rank of the stationary 128-row tile with the
+// tile that meets the most streamed blocks first, z = chunk of streamed blocks.  Blocks are dispatched x-fastest,
+// so the launch walks ALL units' heaviest tiles first and ends on the lightest ones (longest-processing-time-first
+// over the whole launch, not per head): under a causal mask a tile's work ranges from one block to all of them.
+template <int MODE, int BX, int STAGES, bool BF16, bool SOFTCAP, int AUX, bool GROUPED = false>
 __global__ void __launch_bounds__(192, 1)
 attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_x,
                   const __grid_constant__ CUtensorMap tm_n, const SweepParams p) {
@@ -417,11 +540,15 @@ attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   c.abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int chunk = blockIdx.x;
-  c.a0 = blockIdx.y * 128;
-  c.bh = blockIdx.z;
-  c.b = c.bh / p.heads;
-  c.h = c.bh - c.b * p.heads;
+  const int chunk = blockIdx.z;
+  // column sums: key tile 0 meets every query block under a causal mask; row sweep: the last query tile sees every key
+  c.a0 = (MODE == SWEEP_KF_ROWLSE ? (int)(gridDim.y - 1 - blockIdx.y) : (int)blockIdx.y) * 128;
+  c.bh = blockIdx.x;
+  {
+    const int unit_heads = GROUPED ? p.heads / p.kv_group : p.heads;   // GROUPED: one CTA per (batch, K/V head)
+    c.b = c.bh / unit_heads;
+    c.h = c.bh - c.b * unit_heads;
+  }
   if constexpr (MODE == SWEEP_KF_ROWLSE) {
     const int r_last = min(c.a0 + 127, p.q_len - 1);
     c.blk_lo = 0;
@@ -475,7 +602,7 @@ attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       // thread r copies row r of the stationary tile (256 contiguous bytes) from global memory into TMEM lane r;
       // a 32-bit TMEM column holds two consecutive 16-bit elements, which is the order they have in memory
       const int row = c.a0 + (int)threadIdx.x;
-      const int a_head = MODE == SWEEP_KF_ROWLSE ? c.h : c.h / p.kv_group;
+      const int a_head = (GROUPED || MODE == SWEEP_KF_ROWLSE) ? c.h : c.h / p.kv_group;
       const uint4* src = reinterpret_cast<const uint4*>(
           p.a_base + (((int64_t)c.b * p.a_rows + row) * p.a_heads + a_head) * 128);
       const uint32_t dst = c.tmem_base + ((uint32_t)(warp * 32) << 16) + Cfg::A_COL;
@@ -499,12 +626,14 @@ attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     }
     if constexpr (MODE == SWEEP_KF_ROWLSE)
       sweep_compute_rowlse<Cfg>(c, p);
+    else if constexpr (GROUPED)
+      sweep_compute_colsum_grouped<Cfg, SOFTCAP, AUX>(c, p, chunk);
     else
       sweep_compute_colsum<Cfg, SOFTCAP, AUX>(c, p, chunk);
   } else if (warp == 4) {
-    if (lane == 0) sweep_producer<Cfg>(c, p, &tm_a, &tm_x, &tm_n);
+    if (lane == 0) sweep_producer<Cfg, GROUPED>(c, p, &tm_a, &tm_x, &tm_n);
   } else {
-    sweep_mma<Cfg, BF16>(c);
+    sweep_mma<Cfg, BF16>(c, (c.blk_hi - c.blk_lo) * (GROUPED ? p.kv_group : 1));
   }
   tc_fence_before();
   __syncthreads();
@@ -581,11 +710,12 @@ inline int64_t score_workspace_bytes(int batch, int q_len, int kv_len, int heads
   return score_workspace_layout(batch, q_len, kv_len, heads).total;
 }
 
-template <int MODE, int BX, int STAGES, bool BF16, bool SOFTCAP, int AUX>
+// n_chunks chunks of streamed blocks x n_tiles stationary tiles x (batch x heads) units -- (batch x K/V heads) when GROUPED
+template <int MODE, int BX, int STAGES, bool BF16, bool SOFTCAP, int AUX, bool GROUPED = false>
 int launch_sweep(const CUtensorMap& ta, const CUtensorMap& tx, const CUtensorMap& tn, const SweepParams& p,
-                 int grid_x, int grid_y, cudaStream_t stream) {
+                 int n_chunks, int n_tiles, cudaStream_t stream) {
   using Cfg = SweepCfg<MODE, BX, STAGES>;
-  auto kern = attn_sweep_kernel<MODE, BX, STAGES, BF16, SOFTCAP, AUX>;
+  auto kern = attn_sweep_kernel<MODE, BX, STAGES, BF16, SOFTCAP, AUX, GROUPED>;
   static thread_local int configured_dev = -1;
   int dev = 0;
   B200_CUDA_TRY(cudaGetDevice(&dev));
@@ -593,7 +723,7 @@ int launch_sweep(const CUtensorMap& ta, const CUtensorMap& tx, const CUtensorMap
     B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     configured_dev = dev;
   }
-  dim3 grid(grid_x, grid_y, p.batch * p.heads);
+  dim3 grid(p.batch * (GROUPED ? p.heads / p.kv_group : p.heads), n_tiles, n_chunks);
   kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tx, tn, p);
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
@@ -651,12 +781,14 @@ inline int attn_score_impl(const void* q, const void* k, const void* v, void* ou
   if (kv_heads <= 0) kv_heads = heads;
   if (heads % kv_heads != 0) return B200_ERR_BAD_ARGUMENT;
   const int group = heads / kv_heads;
-  // the group mean commutes with the column sum, but not with the square or the Corm threshold test
-  if (group > 1 && (score_sq != nullptr || corm_flags != nullptr)) return B200_ERR_UNSUPPORTED;
   int rc = score_common_checks(q, k, v, out, workspace, workspace_bytes, batch, q_len, kv_len, heads, head_dim, dtype);
   if (rc != B200_OK) return rc;
   if (!score) return B200_ERR_BAD_ARGUMENT;
   if (window > 0 && !causal) return B200_ERR_UNSUPPORTED;
+  if (corm_flags != nullptr && (score_sq != nullptr || softcap > 0.f)) return B200_ERR_BAD_ARGUMENT;
+  // The group mean commutes with the column sum (the ordered reduce adds the g heads' partial vectors), but not
+  // with the square or with Corm's threshold test: those take the grouped sweep, which averages per (key, query).
+  const bool grouped = group > 1 && (score_sq != nullptr || corm_flags != nullptr);
   const ScoreWorkspace w = score_workspace_layout(batch, q_len, kv_len, heads);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   float* lse = reinterpret_cast<float*>(ws + w.lse_off);
@@ -668,7 +800,8 @@ inline int attn_score_impl(const void* q, const void* k, const void* v, void* ou
   const bool bf16 = dtype == B200_BF16;
   CUtensorMap ta, tx, tn;
   if ((rc = make_bshd_tensor_map(&ta, k, batch, kv_len, kv_heads, head_dim, 128, bf16)) != B200_OK) return rc;
-  if ((rc = make_bshd_tensor_map(&tx, q, batch, q_len, heads, head_dim, B200_COLSUM_BX, bf16)) != B200_OK) return rc;
+  if ((rc = make_bshd_tensor_map(&tx, q, batch, q_len, heads, head_dim, grouped ? 64 : B200_COLSUM_BX, bf16)) != B200_OK)
+    return rc;
   tn = ta;  // unused
 
   SweepParams p;
@@ -686,7 +819,7 @@ inline int attn_score_impl(const void* q, const void* k, const void* v, void* ou
   p.lse_stride = w.lse_stride;
   p.kv_pad = w.kv_pad;
   p.n_chunks = w.n_chunks_colsum;
-  p.chunk_blocks = kSweepChunkBlocks * (128 / B200_COLSUM_BX);
+  p.chunk_blocks = kSweepChunkBlocks * (128 / (grouped ? 64 : B200_COLSUM_BX));
   p.a_base = static_cast<const uint16_t*>(k);
   p.a_rows = kv_len;
   p.a_heads = kv_heads;
@@ -696,9 +829,32 @@ inline int attn_score_impl(const void* q, const void* k, const void* v, void* ou
   p.cap_in = softcap > 0.f ? scale / softcap : 0.f;
   p.cap_out = softcap * kLog2e;
   p.inv_tau = 1.0f;
-  if (corm_flags != nullptr && (score_sq != nullptr || softcap > 0.f)) return B200_ERR_BAD_ARGUMENT;
   const bool cap = softcap > 0.f, sq = score_sq != nullptr;
   const int gy = w.kv_pad / 128;
+  if (gy > 65535 || p.n_chunks > 65535) return B200_ERR_UNSUPPORTED;
+
+  if (grouped) {
+    // one CTA per (batch, K/V head, key tile, chunk); 64-query blocks, stationary K tile in TMEM
+#define B200_SWEEPG(BF, CAP, AUXV) \
+  launch_sweep<SWEEP_COLSUM, 64, B200_KF_STAGES, BF, CAP, AUXV, true>(ta, tx, tn, p, p.n_chunks, gy, stream)
+    if (corm_flags != nullptr)
+      rc = bf16 ? B200_SWEEPG(true, false, AUX_CORM) : B200_SWEEPG(false, false, AUX_CORM);
+    else if (bf16)
+      rc = cap ? B200_SWEEPG(true, true, AUX_SQUARES) : B200_SWEEPG(true, false, AUX_SQUARES);
+    else
+      rc = cap ? B200_SWEEPG(false, true, AUX_SQUARES) : B200_SWEEPG(false, false, AUX_SQUARES);
+#undef B200_SWEEPG
+    if (rc != B200_OK) return rc;
+    dim3 ggrid((kv_len + 255) / 256, batch * kv_heads);
+    score_reduce_kernel<<<ggrid, 256, 0, stream>>>(score, score_sq, p.partial, p.partial_sq, kv_len, w.kv_pad,
+                                                   p.n_chunks, 1.0f);
+    B200_CUDA_TRY(cudaGetLastError());
+    if (corm_flags != nullptr) {
+      corm_reduce_kernel<<<ggrid, 256, 0, stream>>>(corm_flags, p.partial_sq, kv_len, w.kv_pad, p.n_chunks);
+      B200_CUDA_TRY(cudaGetLastError());
+    }
+    return B200_OK;
+  }
 
 #define B200_SWEEP0(BF, CAP, AUXV) \
   launch_sweep<SWEEP_COLSUM, B200_COLSUM_BX, B200_COLSUM_STAGES, BF, CAP, AUXV>(ta, tx, tn, p, p.n_chunks, gy, stream)
@@ -724,9 +880,16 @@ inline int attn_score_impl(const void* q, const void* k, const void* v, void* ou
   return B200_OK;
 }
 
+// kv_heads < heads (grouped-query attention): the second softmax is taken per query head against the K/V head it
+// shares, and the score of a K/V head is the mean over its query heads (figure/membound/attn.py:162-165) -- the mean
+// commutes with the sum over the queries, so the ordered reduce adds the g heads' partial vectors and scales by 1/g.
 inline int attn_kf_impl(const void* q, const void* k, const void* v, const float* exp_rand, void* out,
                         float* kf_score, void* workspace, int64_t workspace_bytes, int batch, int q_len, int kv_len,
-                        int heads, int head_dim, int dtype, int causal, float tau, float scale, cudaStream_t stream) {
+                        int heads, int head_dim, int dtype, int causal, float tau, float scale, cudaStream_t stream,
+                        int kv_heads = 0) {
+  if (kv_heads <= 0) kv_heads = heads;
+  if (heads % kv_heads != 0) return B200_ERR_BAD_ARGUMENT;
+  const int group = heads / kv_heads;
   int rc = score_common_checks(q, k, v, out, workspace, workspace_bytes, batch, q_len, kv_len, heads, head_dim, dtype);
   if (rc != B200_OK) return rc;
   if (!exp_rand || !kf_score || !(tau > 0.f)) return B200_ERR_BAD_ARGUMENT;
@@ -737,16 +900,16 @@ inline int attn_kf_impl(const void* q, const void* k, const void* v, const float
   float* lse2 = reinterpret_cast<float*>(ws + w.lse2_off);
 
   // attention output (its own LSE is not needed by the KeyFormer score)
-  rc = attn_fwd_impl_lse_stride(q, k, v, out, nullptr, 0, batch, q_len, kv_len, heads, heads, head_dim, dtype, causal,
-                                0, 0.f, scale, stream);
+  rc = attn_fwd_impl_lse_stride(q, k, v, out, nullptr, 0, batch, q_len, kv_len, heads, kv_heads, head_dim, dtype,
+                                causal, 0, 0.f, scale, stream);
   if (rc != B200_OK) return rc;
 
   const bool bf16 = dtype == B200_BF16;
   CUtensorMap tq128, tk64, tk128, tq64, tn_rows128, tn_rows64;
   if ((rc = make_bshd_tensor_map(&tq128, q, batch, q_len, heads, head_dim, 128, bf16)) != B200_OK) return rc;
   if ((rc = make_bshd_tensor_map(&tq64, q, batch, q_len, heads, head_dim, 64, bf16)) != B200_OK) return rc;
-  if ((rc = make_bshd_tensor_map(&tk128, k, batch, kv_len, heads, head_dim, 128, bf16)) != B200_OK) return rc;
-  if ((rc = make_bshd_tensor_map(&tk64, k, batch, kv_len, heads, head_dim, 64, bf16)) != B200_OK) return rc;
+  if ((rc = make_bshd_tensor_map(&tk128, k, batch, kv_len, kv_heads, head_dim, 128, bf16)) != B200_OK) return rc;
+  if ((rc = make_bshd_tensor_map(&tk64, k, batch, kv_len, kv_heads, head_dim, 64, bf16)) != B200_OK) return rc;
   const int64_t rows = (int64_t)batch * heads * q_len;
   if ((rc = make_f32_matrix_tensor_map(&tn_rows128, exp_rand, rows, kv_len, 128, 32, true)) != B200_OK) return rc;
   if ((rc = make_f32_matrix_tensor_map(&tn_rows64, exp_rand, rows, kv_len, 64, 32, false)) != B200_OK) return rc;
@@ -770,13 +933,14 @@ inline int attn_kf_impl(const void* q, const void* k, const void* v, const float
   p.chunk_blocks = kSweepChunkBlocks;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.inv_tau = 1.0f / tau;
-  p.kv_group = 1;
-  p.a_heads = heads;
+  p.kv_group = group;
 
   // sweep 1: Lz_i = log2 sum_j exp2(z_ij), one CTA per 128 queries
   const int q_tiles = (q_len + 127) / 128;
+  if (q_tiles > 65535 || w.kv_pad / 128 > 65535 || p.n_chunks > 65535) return B200_ERR_UNSUPPORTED;
   p.a_base = static_cast<const uint16_t*>(q);
   p.a_rows = q_len;
+  p.a_heads = heads;
   rc = bf16 ? launch_sweep<SWEEP_KF_ROWLSE, 64, B200_KF_STAGES, true, false, false>(tq128, tk64, tn_rows128, p, 1, q_tiles, stream)
             : launch_sweep<SWEEP_KF_ROWLSE, 64, B200_KF_STAGES, false, false, false>(tq128, tk64, tn_rows128, p, 1, q_tiles, stream);
   if (rc != B200_OK) return rc;
@@ -784,13 +948,14 @@ inline int attn_kf_impl(const void* q, const void* k, const void* v, const float
   const int gy = w.kv_pad / 128;
   p.a_base = static_cast<const uint16_t*>(k);
   p.a_rows = kv_len;
+  p.a_heads = kv_heads;
   rc = bf16 ? launch_sweep<SWEEP_KF_COLSUM, 64, B200_KF_STAGES, true, false, false>(tk128, tq64, tn_rows64, p, p.n_chunks, gy, stream)
             : launch_sweep<SWEEP_KF_COLSUM, 64, B200_KF_STAGES, false, false, false>(tk128, tq64, tn_rows64, p, p.n_chunks, gy, stream);
   if (rc != B200_OK) return rc;
 
-  dim3 rgrid((kv_len + 255) / 256, batch * heads);
-  score_reduce_kernel<<<rgrid, 256, 0, stream>>>(kf_score, nullptr, p.partial, nullptr, kv_len, w.kv_pad, p.n_chunks,
-                                                 1.0f);
+  dim3 rgrid((kv_len + 255) / 256, batch * kv_heads);
+  score_reduce_kernel<<<rgrid, 256, 0, stream>>>(kf_score, nullptr, p.partial, nullptr, kv_len, w.kv_pad,
+                                                 p.n_chunks * group, 1.0f / (float)group);
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
 }

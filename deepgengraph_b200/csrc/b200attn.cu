@@ -132,7 +132,7 @@ const char* b200_status_string(int status) {
 
 int b200_last_cuda_error(void) { return g_last_cuda_error; }
 
-int b200_abi_version(void) { return 1; }
+int b200_abi_version(void) { return 2; }
 
 int b200_device_status(int* status_out) {
   if (!status_out) return B200_ERR_BAD_ARGUMENT;
@@ -298,12 +298,22 @@ int b200_kv_evict_topk(const float* score, const void* k, const void* v, void* k
                             (cudaStream_t)stream);
 }
 
-int b200_attn_score_gqa(const void* q, const void* k, const void* v, void* out, float* score, void* workspace,
-                        int64_t workspace_bytes, int batch, int q_len, int kv_len, int heads, int kv_heads,
-                        int head_dim, int dtype, int causal, int window, float softcap, float scale, void* stream) {
+int b200_attn_score_gqa(const void* q, const void* k, const void* v, void* out, float* score, float* score_sq,
+                        uint8_t* corm_flags, void* workspace, int64_t workspace_bytes, int batch, int q_len,
+                        int kv_len, int heads, int kv_heads, int head_dim, int dtype, int causal, int window,
+                        float softcap, float scale, void* stream) {
   if (kv_heads <= 0) return B200_ERR_BAD_ARGUMENT;
-  return attn_score_impl(q, k, v, out, score, nullptr, workspace, workspace_bytes, batch, q_len, kv_len, heads,
-                         head_dim, dtype, causal, window, softcap, scale, (cudaStream_t)stream, nullptr, kv_heads);
+  return attn_score_impl(q, k, v, out, score, score_sq, workspace, workspace_bytes, batch, q_len, kv_len, heads,
+                         head_dim, dtype, causal, window, softcap, scale, (cudaStream_t)stream, corm_flags, kv_heads);
+}
+
+int b200_attn_kf_score_gqa(const void* q, const void* k, const void* v, const float* exp_rand, void* out,
+                           float* kf_score, void* workspace, int64_t workspace_bytes, int batch, int q_len,
+                           int kv_len, int heads, int kv_heads, int head_dim, int dtype, int causal, float tau,
+                           float scale, void* stream) {
+  if (kv_heads <= 0) return B200_ERR_BAD_ARGUMENT;
+  return attn_kf_impl(q, k, v, exp_rand, out, kf_score, workspace, workspace_bytes, batch, q_len, kv_len, heads,
+                      head_dim, dtype, causal, tau, scale, (cudaStream_t)stream, kv_heads);
 }
 
 int b200_kv_evict_roco(const float* score, const float* score_sq, const void* k, const void* v, void* kv_cache,

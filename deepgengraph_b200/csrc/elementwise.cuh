@@ -305,9 +305,14 @@ int launch_act_and_mul(void* out, const void* in, int64_t num_tokens, int d, cud
 // ---------------------------------------------------------------------------
 // Online rotary embedding (NeoX pairing: element i rotates with element i + D/2),
 // csrc/pos_encoding.cu:83-111.  One warp per token (grid-stride); the D/2 angles
-// are evaluated once per token with accurate powf/sincosf (the reference is built
-// with --use_fast_math; positions of several thousand radians lose most of their
-// precision there), then every head is rotated with 16-byte accesses.
+// are evaluated once per token, then every head is rotated with 16-byte accesses.
+// Angles: the reference computes pos / __powf(theta, 2i/D) and __sincosf of it in
+// fp32 (it is built with --use_fast_math, as this library is); at positions of
+// several thousand radians an fp32 angle alone is off by 5e-4.  Here the inverse
+// frequencies are evaluated once per thread in fp64 (fast-math does not touch
+// double precision), the angle pos * inv_freq and its reduction to [-pi, pi] are
+// fp64 too, and only the reduced angle goes through the fp32 sine / cosine
+// intrinsics, which are accurate to ~5e-7 on that range.
 // ---------------------------------------------------------------------------
 template <typename T, int HEAD_DIM>
 __global__ void __launch_bounds__(256)
@@ -326,12 +331,24 @@ rotary_online_kernel(const int32_t* __restrict__ positions, T* __restrict__ quer
   float* s_sin = s_sin_all[wib];
   const int64_t warp_global = (int64_t)blockIdx.x * WARPS + wib;
   const int64_t warp_count = (int64_t)gridDim.x * WARPS;
+  // inverse frequencies theta^(-2i/D) of the elements this lane evaluates (i = lane, lane + 32, ...), in fp64
+  constexpr int PER_LANE = HALF / 32;
+  double inv_freq[PER_LANE];
+  {
+    const double l2t = log2((double)theta);
+#pragma unroll
+    for (int t = 0; t < PER_LANE; ++t) inv_freq[t] = exp2(-(double)(2 * (lane + 32 * t)) / (double)HEAD_DIM * l2t);
+  }
+  constexpr double kTwoPi = 6.283185307179586476925286766559, kInvTwoPi = 0.15915494309189533576888376337251;
   for (int64_t tok = warp_global; tok < num_tokens; tok += warp_count) {
-    const float pos = (float)positions[tok];
+    const double pos = (double)positions[tok];
     __syncwarp();
-    for (int i = lane; i < HALF; i += 32) {
-      const float freq = pos / powf(theta, (float)(2 * i) / (float)HEAD_DIM);
-      sincosf(freq, &s_sin[i], &s_cos[i]);
+#pragma unroll
+    for (int t = 0; t < PER_LANE; ++t) {
+      const double ang = pos * inv_freq[t];
+      const float r = (float)fma(-kTwoPi, rint(ang * kInvTwoPi), ang);   // in [-pi, pi]
+      s_sin[lane + 32 * t] = __sinf(r);
+      s_cos[lane + 32 * t] = __cosf(r);
     }
     __syncwarp();
     if (vec_ok) {

@@ -307,6 +307,48 @@ kv_evict_roco_kernel(const float* __restrict__ score, const float* __restrict__ 
   gather_selected_rows(s_idx, k, v, kv_cache, b, h, seq, heads, head_dim * ELEM_BYTES, keep);
 }
 
+// Dynamic shared memory beyond which a kernel must opt in (cudaFuncAttributeMaxDynamicSharedMemorySize).  The
+// 48 KB default covers static AND dynamic shared memory together, and both eviction kernels carry about 1 KB of
+// static arrays (histogram, scan scratch), so the opt-in starts well below 48 KB of dynamic memory.
+constexpr size_t kEvictSmemOptIn = 40 * 1024;
+
+template <int ELEM_BYTES>
+int launch_kv_evict_roco(dim3 grid, size_t smem, cudaStream_t stream, const float* score, const float* score_sq,
+                         const void* k, const void* v, void* kv_cache, int32_t* indices, int seq, int heads,
+                         int head_dim, int q_len, int budget, int recent, int staged) {
+  auto kern = kv_evict_roco_kernel<ELEM_BYTES>;
+  static thread_local int configured_dev = -1;   // one per instantiation: every kernel needs its own attribute call
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (smem > kEvictSmemOptIn && configured_dev != dev) {
+    B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    configured_dev = dev;
+  }
+  kern<<<grid, kEvictThreads, smem, stream>>>(score, score_sq, (const uint8_t*)k, (const uint8_t*)v,
+                                              (uint8_t*)kv_cache, indices, seq, heads, head_dim, (float)q_len, budget,
+                                              recent, staged);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+template <int ELEM_BYTES>
+int launch_kv_evict_topk(dim3 grid, size_t smem, cudaStream_t stream, const float* score, const void* k,
+                         const void* v, void* kv_cache, int32_t* indices, int seq, int heads, int head_dim,
+                         int budget, int staged) {
+  auto kern = kv_evict_topk_kernel<ELEM_BYTES>;
+  static thread_local int configured_dev = -1;
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (smem > kEvictSmemOptIn && configured_dev != dev) {
+    B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    configured_dev = dev;
+  }
+  kern<<<grid, kEvictThreads, smem, stream>>>(score, (const uint8_t*)k, (const uint8_t*)v, (uint8_t*)kv_cache, indices,
+                                              seq, heads, head_dim, budget, staged);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
 inline int kv_evict_roco_impl(const float* score, const float* score_sq, const void* k, const void* v,
                               void* kv_cache, int32_t* indices, int batch, int seq, int heads, int head_dim,
                               int q_len, int budget, int recent, int elem_bytes, cudaStream_t stream) {
@@ -321,21 +363,11 @@ inline int kv_evict_roco_impl(const float* score, const float* score_sq, const v
   const int staged = smem_min + (size_t)seq * 8 <= 200 * 1024 ? 1 : 0;
   const size_t smem = smem_min + (staged ? (size_t)seq * 8 : 0);
   const dim3 grid(batch * heads, evict_ctas_per_head(batch * heads));
-  auto launch = [&](auto kern) -> int {
-    static thread_local int configured_dev = -1;
-    int dev = 0;
-    B200_CUDA_TRY(cudaGetDevice(&dev));
-    if (smem > 48 * 1024 && configured_dev != dev) {
-      B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-      configured_dev = dev;
-    }
-    kern<<<grid, kEvictThreads, smem, stream>>>(score, score_sq, (const uint8_t*)k, (const uint8_t*)v,
-                                                (uint8_t*)kv_cache, indices, seq, heads, head_dim, (float)q_len,
-                                                budget, recent, staged);
-    B200_CUDA_TRY(cudaGetLastError());
-    return B200_OK;
-  };
-  return elem_bytes == 2 ? launch(kv_evict_roco_kernel<2>) : launch(kv_evict_roco_kernel<4>);
+  return elem_bytes == 2
+             ? launch_kv_evict_roco<2>(grid, smem, stream, score, score_sq, k, v, kv_cache, indices, seq, heads,
+                                       head_dim, q_len, budget, recent, staged)
+             : launch_kv_evict_roco<4>(grid, smem, stream, score, score_sq, k, v, kv_cache, indices, seq, heads,
+                                       head_dim, q_len, budget, recent, staged);
 }
 
 inline int kv_evict_topk_impl(const float* score, const void* k, const void* v, void* kv_cache, int32_t* indices,
@@ -352,20 +384,10 @@ inline int kv_evict_topk_impl(const float* score, const void* k, const void* v, 
   const int staged = smem_idx + (size_t)seq * 4 <= 200 * 1024 ? 1 : 0;
   const size_t smem = smem_idx + (staged ? (size_t)seq * 4 : 0);
   const dim3 grid(batch * heads, evict_ctas_per_head(batch * heads));
-  auto launch = [&](auto kern) -> int {
-    static thread_local int configured_dev = -1;
-    int dev = 0;
-    B200_CUDA_TRY(cudaGetDevice(&dev));
-    if (smem > 48 * 1024 && configured_dev != dev) {
-      B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-      configured_dev = dev;
-    }
-    kern<<<grid, kEvictThreads, smem, stream>>>(score, (const uint8_t*)k, (const uint8_t*)v, (uint8_t*)kv_cache, indices,
-                                                seq, heads, head_dim, budget, staged);
-    B200_CUDA_TRY(cudaGetLastError());
-    return B200_OK;
-  };
-  return elem_bytes == 2 ? launch(kv_evict_topk_kernel<2>) : launch(kv_evict_topk_kernel<4>);
+  return elem_bytes == 2 ? launch_kv_evict_topk<2>(grid, smem, stream, score, k, v, kv_cache, indices, seq, heads,
+                                                   head_dim, budget, staged)
+                         : launch_kv_evict_topk<4>(grid, smem, stream, score, k, v, kv_cache, indices, seq, heads,
+                                                   head_dim, budget, staged);
 }
 
 }  // namespace b200

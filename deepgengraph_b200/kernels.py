@@ -20,6 +20,29 @@ def _default_device():
   return torch.device("cuda", torch.cuda.current_device())
 
 
+def check_corm_mask(corm_mask, q_len, kv_len):
+  """The Corm kernel evaluates the thresholds of Corm.prepare (row i = 1 / (i + 1), kernels/corm.py:47-49) itself.
+  The reference compares against whatever [q_len, kv_len] tensor the caller passes (kernels/corm.py:35-37), so a
+  mask with other values cannot be honoured: it is refused instead of being ignored."""
+  if corm_mask is None:
+    return
+  tag = (corm_mask.data_ptr(), corm_mask._version, tuple(corm_mask.shape), q_len, kv_len)
+  if tag == _checked_corm_mask[0]:     # the same tensor, unmodified since it was checked: no second device round trip
+    return
+  if tuple(corm_mask.shape) != (q_len, kv_len):
+    raise NotImplementedError(f"corm_mask must be [q_len, kv_len] = [{q_len}, {kv_len}], got {tuple(corm_mask.shape)}")
+  want = 1.0 / torch.arange(1, q_len + 1, dtype=torch.float32, device=corm_mask.device)
+  # row i is constant: its first and last columns and one full diagonal sample pin the whole tensor cheaply
+  cols = corm_mask[:, [0, kv_len - 1]].float()
+  diag = corm_mask[torch.arange(q_len, device=corm_mask.device), torch.arange(q_len, device=corm_mask.device) % kv_len].float()
+  if not (torch.equal(cols[:, 0], want) and torch.equal(cols[:, 1], want) and torch.equal(diag, want)):
+    raise NotImplementedError("corm_mask differs from the thresholds 1 / (i + 1) that the fused Corm kernel evaluates")
+  _checked_corm_mask[0] = tag
+
+
+_checked_corm_mask = [None]
+
+
 class _CoreModule(nn.Module):
   def __init__(self, kv_head_num=32, head_num=32, head_dim=128):
     super().__init__()
@@ -150,6 +173,7 @@ class Corm(_CoreModule):
     assert self.group_size == 1
 
   def forward(self, q, k, v, corm_mask=None):
+    check_corm_mask(corm_mask, q.shape[1], k.shape[1])
     return _att.attn_corm_fwd(q, k, v, causal=True)
 
   def prepare(self, batch_size=1, q_len=4096, kv_len=4096, dtype=torch.float16, device=None):

@@ -52,25 +52,29 @@ def shard_pieces(batch: int, kv_heads: int, world: int, rank: int) -> List[Piece
   return pieces
 
 
-def slice_piece(q, k, v, piece: Piece, group: int, extra=None):
-  """Contiguous BSHD views-made-dense of one piece: q heads [hk_lo*group, hk_hi*group), kv heads [hk_lo, hk_hi).
-  `extra` (optional) is a [B, H, Sq, Skv] tensor sliced the same way (KeyFormer's exp_rand)."""
+def slice_piece(q, k, v, piece: Piece, group: int, extra=None, dense: bool = True):
+  """One piece of the problem: q heads [hk_lo*group, hk_hi*group), kv heads [hk_lo, hk_hi) of batch element b, BSHD.
+  dense=True copies the slices into contiguous tensors (what the score variants take); dense=False returns the head
+  slices as VIEWS -- attention.attn_fwd reads such row-strided views through its TMA descriptors, so a shard of the
+  plain attention costs no copy.  `extra` (optional) is a [B, H, Sq, Skv] tensor sliced the same way (KeyFormer's
+  exp_rand; always contiguous, a head range of it already is)."""
   b, lo, hi = piece.b, piece.hk_lo, piece.hk_hi
-  qs = q[b:b + 1, :, lo * group:hi * group].contiguous()
-  ks = k[b:b + 1, :, lo:hi].contiguous()
-  vs = v[b:b + 1, :, lo:hi].contiguous()
+  qs, ks, vs = q[b:b + 1, :, lo * group:hi * group], k[b:b + 1, :, lo:hi], v[b:b + 1, :, lo:hi]
+  if dense:
+    qs, ks, vs = qs.contiguous(), ks.contiguous(), vs.contiguous()
   if extra is None:
     return qs, ks, vs
   return qs, ks, vs, extra[b:b + 1, lo * group:hi * group].contiguous()
 
 
-def run_sharded(fn, q, k, v, world: int, rank: int, extra=None):
+def run_sharded(fn, q, k, v, world: int, rank: int, extra=None, dense: bool = True):
   """Runs `fn(q_piece, k_piece, v_piece[, extra_piece])` on this rank's pieces of the full problem.
-  Returns a list of (piece, result) -- results stay on the device, sharded."""
+  Returns a list of (piece, result) -- results stay on the device, sharded.  dense=False hands `fn` views
+  (for attention.attn_fwd, which needs no copy)."""
   group = q.size(2) // k.size(2)
   out = []
   for piece in shard_pieces(q.size(0), k.size(2), world, rank):
-    args = slice_piece(q, k, v, piece, group, extra)
+    args = slice_piece(q, k, v, piece, group, extra, dense)
     out.append((piece, fn(*args)))
   return out
 

@@ -5,9 +5,11 @@
  * Every entry point takes plain device pointers, sizes and a CUDA stream
  * (passed as void*, may be NULL for the legacy default stream), enqueues its
  * kernels on that stream and returns without synchronising.  The return value
- * is a b200_status code (0 = success); nothing throws and nothing allocates
+ * is a b200_status code (0 = success); nothing throws and no call allocates
  * device memory: scratch buffers are sized by the *_workspace_bytes queries and
- * supplied by the caller.
+ * supplied by the caller.  (The library image itself carries two fixed device
+ * arrays per GPU that loads it: the 32 MiB scratch of b200_attn_score_static and
+ * a small pool of scheduler counters.)
  *
  * Tensor layouts follow the reference project (DeepGenGroup/DeepGenGraph):
  *   q            [batch, q_len,  heads,    head_dim]   ("BSHD", contiguous)
@@ -158,18 +160,18 @@ int b200_attn_score(const void* q, const void* k, const void* v, void* out, floa
                     int window, float softcap, float scale, void* stream);
 
 /*
- * b200_attn_score for grouped-query attention (heads > kv_heads): the probabilities are averaged over the
- * heads / kv_heads query heads that share a K/V head before they are summed over the queries
- *   -- the group_size > 1 branch of kernels/roco.py:39-40 and figure/membound/attn.py:84-88 (the reference's
- *      modules assert group_size == 1, so that branch never runs there).
- * k, v   [batch, kv_len, kv_heads, head_dim];  score float32 [batch, kv_heads, kv_len].
+ * b200_attn_score / b200_attn_corm for grouped-query attention (heads > kv_heads): every statistic is taken from
+ * the probabilities AVERAGED over the heads / kv_heads query heads that share a K/V head
+ *   pm_ij = mean_h p^h_ij;  score_j = sum_i pm_ij;  score_sq_j = sum_i pm_ij^2;  corm_j = any_i(pm_ij >= 1/(i+1))
+ *   -- the group_size > 1 branches of kernels/roco.py:25-27,39-46 and figure/membound/attn.py:84-88,123-131,240-244
+ *      (the modules under kernels/ assert group_size == 1; the ones under figure/membound run it).
+ * k, v   [batch, kv_len, kv_heads, head_dim];  score, score_sq float32 and corm_flags uint8 [batch, kv_heads, kv_len].
+ * score_sq and corm_flags are optional (NULL) and exclusive; corm_flags needs softcap == 0.
  * The workspace is sized for `heads` (b200_attn_score_workspace_bytes(batch, q_len, kv_len, heads)).
- * Only the plain column sums are offered: the mean over the group does not commute with the square
- * (RoCo's second statistic), which returns B200_ERR_UNSUPPORTED for heads != kv_heads.
  */
-int b200_attn_score_gqa(const void* q, const void* k, const void* v, void* out, float* score,
-                        void* workspace, int64_t workspace_bytes, int batch, int q_len, int kv_len,
-                        int heads, int kv_heads, int head_dim, int dtype, int causal, int window,
+int b200_attn_score_gqa(const void* q, const void* k, const void* v, void* out, float* score, float* score_sq,
+                        uint8_t* corm_flags, void* workspace, int64_t workspace_bytes, int batch, int q_len,
+                        int kv_len, int heads, int kv_heads, int head_dim, int dtype, int causal, int window,
                         float softcap, float scale, void* stream);
 
 /*
@@ -190,6 +192,8 @@ int b200_attn_score_gqa(const void* q, const void* k, const void* v, void* out, 
  *  - All calls on a device share the one array, which keeps the previous call's contents.  Nothing in it has
  *    to start at zero (every element that is read is written earlier in the same call), but two calls that
  *    overlap on the GPU (for example on different streams) race on it: serialise them.
+ *  - batch, q_len, kv_len and heads must be positive: an empty problem returns B200_ERR_BAD_ARGUMENT here
+ *    (as it does at b200_attn_score) and launches nothing.
  */
 int b200_attn_score_static(const void* q, const void* k, const void* v, void* out, float* score,
                            float* score_sq, int batch, int q_len, int kv_len, int heads, int head_dim,
@@ -254,6 +258,16 @@ int b200_attn_kf_score(const void* q, const void* k, const void* v, const float*
                        void* out, float* kf_score, void* workspace, int64_t workspace_bytes,
                        int batch, int q_len, int kv_len, int heads, int head_dim, int dtype,
                        int causal, float tau, float scale, void* stream);
+
+/*
+ * b200_attn_kf_score for grouped-query attention: exp_rand stays [batch, heads, q_len, kv_len] (one noise plane per
+ * QUERY head), k, v are [batch, kv_len, kv_heads, head_dim], and kf_score float32 [batch, kv_heads, kv_len] is the
+ * mean over the query heads of a K/V head of their column sums -- figure/membound/attn.py:162-165.
+ */
+int b200_attn_kf_score_gqa(const void* q, const void* k, const void* v, const float* exp_rand, void* out,
+                           float* kf_score, void* workspace, int64_t workspace_bytes, int batch, int q_len,
+                           int kv_len, int heads, int kv_heads, int head_dim, int dtype, int causal, float tau,
+                           float scale, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,12 +1,13 @@
-"""CPU restatement (PyTorch, fp32/fp64) of the reference's hot-path math.
+"""CPU restatement (PyTorch, fp32/fp64) of the reference's hot-path math.  Every function computes on the device
+of its inputs, so a test may also evaluate it with plain fp32 torch on a GPU for the full-size configurations
+(per batch element and head chunk, which bounds the [heads, Sq, Skv] temporaries).
 
 THIS FILE IS TEST INFRASTRUCTURE.  Only tests/, __graft_entry__.smoke() and the cpu_baseline /
 reference arms of bench.py may import it; the product (deepgengraph_b200/) never does.
 
 Parity pin: every function below that has a counterpart among the reference's PyTorch modules
 is checked in tests/test_oracle.py against golden outputs produced by importing and running
-those modules themselves (tests/golden/make_golden.py, run inside the build container where
-the reference tree is mounted).  The csrc/ ops (RMSNorm, SiLU-gate, RoPE) are CUDA sources in
+those modules themselves (tests/golden/make_golden.py, which needs the reference tree).  The csrc/ ops (RMSNorm, SiLU-gate, RoPE) are CUDA sources in
 the reference; their restatements here are additionally compared on the GPU with the
 reference kernels themselves when oracle/_ref holds a build of them (oracle/build_ref.py).
 Features with no reference code at all (sliding window, grouped-query attention, head_dim 256,
@@ -54,29 +55,40 @@ def attention_ref(q, k, v, causal=True, window=0, softcap=0.0, scale=None, exp_r
     snapkv    [B, H, Skv]    fp32   snapkv.py:36-38 avg_pool1d(colsum, kernel 5, padding 2, stride 1)
     corm      [B, H, Skv]    bool   corm.py:35-37  any over queries of probs >= 1 / (i + 1)
   softcap > 0: scores = tanh(scores / softcap) * softcap after the scale, before the mask (gemma2.py:30-34).
-  Grouped-query attention (H > Hk) expands k/v per group like roco.py:25-27.
+  Grouped-query attention (H > Hk) expands k/v per group like roco.py:25-27, and every per-key statistic is
+  taken from the probabilities AVERAGED over the H / Hk query heads of a K/V head (roco.py:39-40,
+  figure/membound/attn.py:84-88,123-124,162-164,200-204): the score entries are then [B, Hk, Skv].
+  (figure/membound/attn.py:240-244 computes Corm's group mean and then thresholds the un-averaged
+  probabilities, after which its view to [B, Hk, Skv] cannot succeed; the restatement here thresholds the mean.)
   """
   in_dtype = q.dtype
   B, Sq, H, D = q.shape
   Skv, Hk = k.shape[1], k.shape[2]
   g = H // Hk
   scale = scale if scale else 1.0 / math.sqrt(D)
-  vis = _visible_mask(Sq, Skv, causal, window, q.device)
+  dev = q.device
+  vis = _visible_mask(Sq, Skv, causal, window, dev)
   res = {}
   if "out" in want:
-    res["out"] = torch.empty(B, Sq, H, D, dtype=torch.float32)
+    res["out"] = torch.empty(B, Sq, H, D, dtype=torch.float32, device=dev)
   if "lse2" in want:
-    res["lse2"] = torch.empty(B, H, Sq, dtype=torch.float32)
+    res["lse2"] = torch.empty(B, H, Sq, dtype=torch.float32, device=dev)
   for name in ("colsum", "colsum_sq", "kf", "snapkv"):
     if name in want:
-      res[name] = torch.empty(B, H, Skv, dtype=torch.float32)
+      res[name] = torch.empty(B, Hk, Skv, dtype=torch.float32, device=dev)
   if "corm" in want:
-    res["corm"] = torch.empty(B, H, Skv, dtype=torch.bool)
+    res["corm"] = torch.empty(B, Hk, Skv, dtype=torch.bool, device=dev)
+  head_chunk = max(g, head_chunk // g * g)        # whole groups per chunk
+
+  def group_mean(t):                              # [h, Sq, Skv] -> [h / g, Sq, Skv]
+    return t if g == 1 else t.reshape(t.shape[0] // g, g, Sq, Skv).mean(dim=1)
+
   for b in range(B):
     for h0 in range(0, H, head_chunk):
       h1 = min(H, h0 + head_chunk)
+      k0, k1 = h0 // g, h1 // g
       qh = q[b, :, h0:h1].float().transpose(0, 1)                       # [h, Sq, D]
-      kv_idx = torch.arange(h0, h1) // g
+      kv_idx = torch.arange(h0, h1, device=dev) // g
       kh = k[b][:, kv_idx].float().transpose(0, 1)                      # [h, Skv, D]
       vh = v[b][:, kv_idx].float().transpose(0, 1)
       scores = torch.matmul(qh, kh.transpose(-2, -1)) * scale           # attn.py:29
@@ -89,19 +101,20 @@ def attention_ref(q, k, v, causal=True, window=0, softcap=0.0, scale=None, exp_r
         res["out"][b, :, h0:h1] = torch.matmul(p_lo, vh).transpose(0, 1)  # attn.py:32-34
       if "lse2" in want:
         res["lse2"][b, h0:h1] = torch.logsumexp(scores, dim=-1) / math.log(2.0)
+      pm = group_mean(probs) if any(n in want for n in ("colsum", "colsum_sq", "snapkv", "corm")) else None
       if "colsum" in want:
-        res["colsum"][b, h0:h1] = probs.sum(dim=1)                      # h2o.py:35-36 (sum over queries)
+        res["colsum"][b, k0:k1] = pm.sum(dim=1)                         # h2o.py:35-36 (sum over queries)
       if "colsum_sq" in want:
-        res["colsum_sq"][b, h0:h1] = (probs ** 2).sum(dim=1)            # roco.py:43-46
+        res["colsum_sq"][b, k0:k1] = (pm ** 2).sum(dim=1)               # roco.py:39-46 (mean, then square)
       if "snapkv" in want:
-        res["snapkv"][b, h0:h1] = F.avg_pool1d(probs.sum(dim=1)[None], kernel_size=5, padding=2, stride=1)[0]
+        res["snapkv"][b, k0:k1] = F.avg_pool1d(pm.sum(dim=1)[None], kernel_size=5, padding=2, stride=1)[0]
       if "corm" in want:
-        thr = 1.0 / torch.arange(1, Sq + 1, dtype=torch.float32)[:, None]   # corm.py:47-49
-        res["corm"][b, h0:h1] = (probs >= thr).any(dim=1)
+        thr = 1.0 / torch.arange(1, Sq + 1, dtype=torch.float32, device=dev)[:, None]   # corm.py:47-49
+        res["corm"][b, k0:k1] = (pm >= thr).any(dim=1)
       if "kf" in want:
         gumbels = -exp_rand[b, h0:h1].float().log()                     # kf.py:36-37
         z = (scores + gumbels) / tau                                    # kf.py:38 (masked entries stay -inf)
-        res["kf"][b, h0:h1] = F.softmax(z, dim=-1).sum(dim=1)           # kf.py:39-40
+        res["kf"][b, k0:k1] = group_mean(F.softmax(z, dim=-1)).sum(dim=1)   # kf.py:39-40
   return res
 
 
@@ -187,7 +200,7 @@ def rotary_online_ref(positions, query, key, head_dim, theta):
   Angles in fp64 (the reference's fast-math __powf/__sincosf are an approximation of this).
   Returns rotated (query, key) in fp32, same shapes as the inputs ([T, heads*D])."""
   half = head_dim // 2
-  i = torch.arange(half, dtype=torch.float64)
+  i = torch.arange(half, dtype=torch.float64, device=positions.device)
   inv_freq = 1.0 / (float(theta) ** (2.0 * i / head_dim))
   ang = positions.double()[:, None] * inv_freq[None, :]          # [T, D/2]
   cos, sin = ang.cos(), ang.sin()
@@ -221,7 +234,7 @@ def gemma2_layer_ref(x, w, cfg):
   h = rms_norm_ref(x, w["ln1"], cfg["eps"]).to(dt)
   qkv = lin(h, w["qkv"])
   q, k, v = qkv.split([H * D, Hk * D, Hk * D], dim=-1)
-  pos = torch.arange(S, dtype=torch.int32).repeat(B)
+  pos = torch.arange(S, dtype=torch.int32, device=x.device).repeat(B)
   qr, kr = rotary_online_ref(pos, q.reshape(B * S, H * D), k.reshape(B * S, Hk * D), D, cfg["rope_theta"])
   qr, kr = qr.to(dt).view(B, S, H, D), kr.to(dt).view(B, S, Hk, D)
   a = attention_ref(qr, kr, v.reshape(B, S, Hk, D), causal=True, window=cfg["window"], softcap=cfg["softcap"],
@@ -233,3 +246,29 @@ def gemma2_layer_ref(x, w, cfg):
   act = gelu_tanh_and_mul_ref(gu).to(dt)
   dn = lin(act, w["down"])
   return (x1.float() + dn.float()).to(dt).float()
+
+
+def gemma2_layer_ref_fp32(x, w, cfg, head_chunk=2):
+  """The same layer evaluated in fp32 end to end: the stored (16-bit) values of x and of the weights are upcast once
+  and NOTHING is rounded afterwards -- the fp32 reference that a 16-bit pipeline is held against at
+  rtol = atol = 2e-2.  Computes on the device of x.  Returns fp32 [B, S, hidden]."""
+  B, S, hidden = x.shape
+  H, Hk, D = cfg["heads"], cfg["kv_heads"], cfg["head_dim"]
+  xf = x.float()
+  wf = {k: t.float() for k, t in w.items()}
+
+  def norm(t, weight):                                    # csrc/norm.cu:42-55 without the two roundings to T
+    return t * torch.rsqrt(t.pow(2).mean(dim=-1, keepdim=True) + cfg["eps"]) * weight
+
+  h = norm(xf, wf["ln1"])
+  qkv = h @ wf["qkv"].t()
+  q, k, v = qkv.split([H * D, Hk * D, Hk * D], dim=-1)
+  pos = torch.arange(S, dtype=torch.int32, device=x.device).repeat(B)
+  qr, kr = rotary_online_ref(pos, q.reshape(B * S, H * D), k.reshape(B * S, Hk * D), D, cfg["rope_theta"])
+  a = attention_ref(qr.view(B, S, H, D), kr.view(B, S, Hk, D), v.reshape(B, S, Hk, D), causal=True,
+                    window=cfg["window"], softcap=cfg["softcap"], want=("out",), head_chunk=head_chunk)["out"]
+  x1 = xf + a.reshape(B, S, H * D) @ wf["o"].t()
+  gu = norm(x1, wf["ln2"]) @ wf["gate_up"].t()
+  d = gu.shape[-1] // 2
+  act = F.gelu(gu[..., :d], approximate="tanh") * gu[..., d:]
+  return x1 + act @ wf["down"].t()

@@ -24,7 +24,7 @@ def lcg_grid(shape, seed, lo=-2.0, step=1.0 / 64, levels=257):
   return out.reshape(shape)
 
 
-# name -> dict(model, ctor kwargs, B, Sq, Skv, H, D, q_gain)
+# name -> dict(model, ctor kwargs, B, Sq, Skv, H[, Hk], D, q_gain[, source])
 CASES = {
     "attn_s192": dict(model="attn", B=1, Sq=192, Skv=192, H=2, D=128),
     "attn_sq128_skv320": dict(model="attn", B=1, Sq=128, Skv=320, H=2, D=128),
@@ -37,6 +37,12 @@ CASES = {
     "kf_s256_tau1": dict(model="kf", B=1, Sq=256, Skv=256, H=2, D=128, tau=1.0),
     "snapkv_s192": dict(model="snapkv", B=1, Sq=192, Skv=192, H=2, D=128),
     "corm_s192": dict(model="corm", B=1, Sq=192, Skv=192, H=2, D=128),
+    # grouped-query attention (Hk < H): produced by the reference's GQA-capable module variants
+    # (deepgengraph_exp/figure/membound/attn.py), whose scores are the group mean of the probabilities
+    "attn_gqa_s192": dict(model="attn", B=1, Sq=192, Skv=192, H=4, Hk=2, D=128, source="membound"),
+    "h2o_gqa_s192": dict(model="h2o", B=1, Sq=192, Skv=192, H=4, Hk=2, D=128, source="membound"),
+    "roco_gqa_sq128_skv256": dict(model="roco", B=2, Sq=128, Skv=256, H=6, Hk=2, D=128, source="membound"),
+    "snapkv_gqa_s192": dict(model="snapkv", B=1, Sq=192, Skv=192, H=4, Hk=1, D=128, source="membound"),
 }
 
 
@@ -45,9 +51,10 @@ def make_inputs(name, dtype=torch.float32):
   c = CASES[name]
   seed = sum(ord(ch) * (i + 1) for i, ch in enumerate(name))
   B, Sq, Skv, H, D = c["B"], c["Sq"], c["Skv"], c["H"], c["D"]
+  Hk = c.get("Hk", H)
   q = lcg_grid((B, Sq, H, D), seed + 1) * c.get("q_gain", 1.0)
-  k = lcg_grid((B, Skv, H, D), seed + 2)
-  v = lcg_grid((B, Skv, H, D), seed + 3)
+  k = lcg_grid((B, Skv, Hk, D), seed + 2)
+  v = lcg_grid((B, Skv, Hk, D), seed + 3)
   out = {"q": torch.from_numpy(q).to(dtype), "k": torch.from_numpy(k).to(dtype), "v": torch.from_numpy(v).to(dtype)}
   if c["model"] == "kf":
     # strictly positive, exactly representable: 1/256 .. 4

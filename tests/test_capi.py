@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_status_strings_and_version():
   lib = _lib.load()
-  assert lib.b200_abi_version() == 1
+  assert lib.b200_abi_version() == 2
   assert lib.b200_status_string(0) == b"ok"
   assert b"unsupported" in lib.b200_status_string(4)
 

@@ -295,3 +295,15 @@ def test_host_validation(cuda_device):
     att.attn_fwd(q.cpu(), k.cpu(), v.cpu())
   with pytest.raises(RuntimeError):   # unsupported head_dim comes back as a status code from the C ABI
     att.attn_fwd(q[..., :64].contiguous(), k[..., :64].contiguous(), v[..., :64].contiguous())
+
+
+def test_head_sliced_views_give_the_bits_of_the_full_problem(cuda_device):
+  # a rank's shard of the plain attention is a head range of the full tensors: attn_fwd reads it as a view (no copy)
+  # and, a unit's result not depending on its neighbours, returns the bits of the one-GPU run
+  from deepgengraph_b200 import sharding as sh
+  q, k, v = (t.to(cuda_device) for t in _qkv(2, 640, 640, 12, 4, 128, torch.bfloat16, seed=91))
+  full = att.attn_fwd(q, k, v)
+  world = 3
+  for rank in range(world):
+    for piece, out in sh.run_sharded(lambda a, b, c: att.attn_fwd(a, b, c), q, k, v, world, rank, dense=False):
+      assert torch.equal(out[0], full[piece.b, :, piece.hk_lo * 3:piece.hk_hi * 3])

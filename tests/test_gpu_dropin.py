@@ -83,3 +83,41 @@ def test_nvtx_ranges_do_not_change_results(cuda_device):
   finally:
     tracing.enable(False)
   assert torch.equal(got, want)
+
+
+def test_prepare_draws_the_reference_distributions(cuda_device):
+  # Attn draws q, k, v from U[0, 1) (kernels/attn.py:38-40); every other module from N(0, 1); KeyFormer's exp_rand is
+  # 1 + |N(0, 1)| (kernels/kf.py:48); Corm's mask holds 1 / (i + 1) in row i (kernels/corm.py:47-49)
+  torch.manual_seed(0)
+  for name, cls in KERNEL_ZOO.items():
+    spec = cls(kv_head_num=2, head_num=2, head_dim=128).prepare(batch_size=1, q_len=1024, kv_len=1024, dtype=torch.float16)
+    for key in ("q", "k", "v"):
+      t = spec["input"][key].float()
+      assert t.is_cuda and tuple(t.shape) == (1, 1024, 2, 128)
+      if name == "attn":
+        assert t.min().item() >= 0.0 and t.max().item() < 1.0 and abs(t.mean().item() - 0.5) < 0.01
+        assert abs(t.var().item() - 1.0 / 12.0) < 0.01
+      else:
+        assert abs(t.mean().item()) < 0.02 and abs(t.std().item() - 1.0) < 0.02 and t.min().item() < -3.0
+    if name == "kf":
+      er = spec["input"]["exp_rand"]
+      assert er.dtype == torch.float32 and tuple(er.shape) == (1, 2, 1024, 1024) and er.min().item() >= 1.0
+      assert abs((er - 1).mean().item() - (2.0 / 3.141592653589793) ** 0.5) < 0.01      # mean of |N(0, 1)|
+    if name == "corm":
+      m = spec["input"]["corm_mask"]
+      assert tuple(m.shape) == (1024, 1024)
+      torch.testing.assert_close(m[:, 0].cpu(), 1.0 / torch.arange(1, 1025, dtype=torch.float32))
+
+
+def test_corm_with_foreign_thresholds_is_refused(cuda_device):
+  # the kernel evaluates the thresholds 1 / (i + 1) itself; a caller that passes any other corm_mask must hear about it
+  model = KERNEL_ZOO["corm"](kv_head_num=2, head_num=2, head_dim=128)
+  spec = model.prepare(batch_size=1, q_len=256, kv_len=256, dtype=torch.float16)
+  names = list(spec["input"].keys())
+  inputs = [spec["input"][n] for n in names]
+  f = b200_compile(model, names, inputs, spec["output"], system="b200")
+  f(*inputs)
+  with pytest.raises(NotImplementedError):
+    f(inputs[0], inputs[1], inputs[2], inputs[3] * 0.5)
+  with pytest.raises(NotImplementedError):
+    model(inputs[0], inputs[1], inputs[2], inputs[3][:, :128].contiguous())

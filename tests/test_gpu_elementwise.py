@@ -64,10 +64,25 @@ def test_rotary_embedding_online_in_place(cuda_device, dtype, tokens, heads, kv_
   ref_q, ref_k = rm.rotary_online_ref(pos, q, k, head_dim, 10000.0)
   qd, kd = q.to(cuda_device), k.to(cuda_device)
   ops.rotary_embedding_online(pos.to(cuda_device), qd, kd, head_dim, 10000.0)
-  # the result is the fp64-angle rotation rounded to T; fp32 angles at position 8191 lose ~1e-3 absolute
-  tol = dict(rtol=max(TOL[dtype]["rtol"], 2e-3), atol=max(TOL[dtype]["atol"], 4e-3))
+  # the result is the fp64-angle rotation rounded to T: angles and their range reduction are fp64 in the kernel,
+  # so fp32 data at position 8191 (angles of thousands of radians) agree with the fp64 oracle to 2e-5
+  tol = TOL[dtype] if dtype != torch.float32 else dict(rtol=1e-5, atol=2e-5)
   torch.testing.assert_close(qd.float().cpu(), ref_q, **tol)
   torch.testing.assert_close(kd.float().cpu(), ref_k, **tol)
+
+
+def test_rotary_fp32_at_the_largest_positions_is_accurate(cuda_device):
+  # every token sits at a position of thousands of radians for the lowest frequencies' neighbours; an fp32 angle
+  # alone would be off by 5e-4 there (and the reference's fast-math build by ~1e-3)
+  T, H, D = 64, 2, 256
+  q = _gen((T, H * D), torch.float32, 21)
+  k = _gen((T, H * D), torch.float32, 22)
+  pos = torch.arange(8191 - T + 1, 8192, dtype=torch.int32)
+  ref_q, ref_k = rm.rotary_online_ref(pos, q, k, D, 10000.0)
+  qd, kd = q.to(cuda_device), k.to(cuda_device)
+  ops.rotary_embedding_online(pos.to(cuda_device), qd, kd, D, 10000.0)
+  torch.testing.assert_close(qd.cpu(), ref_q, rtol=0, atol=2e-5)
+  torch.testing.assert_close(kd.cpu(), ref_k, rtol=0, atol=2e-5)
 
 
 def test_rotary_on_strided_rows(cuda_device):

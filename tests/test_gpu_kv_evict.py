@@ -100,3 +100,35 @@ def test_vectors_too_long_for_shared_memory_staging(cuda_device):
   cache, idx = att.kv_evict_roco(score.to(cuda_device), score_sq.to(cuda_device), k.to(cuda_device), k.to(cuda_device),
                                  Sq, 200, 20, return_indices=True)
   assert torch.equal(idx.cpu().long(), ref_idx) and torch.equal(cache.cpu(), ref_cache)
+
+
+@pytest.mark.parametrize("seq,budget", [(12000, 100), (12032, 12), (39936, 12288), (50000, 12288)])
+def test_shared_memory_sizes_around_the_opt_in_threshold(cuda_device, seq, budget):
+  # dynamic shared memory = 4 * budget (+ 4 * seq while the keys fit): 48 400 B, 48 176 B (just under 48 KB, where the
+  # static arrays push the total over the default limit), 208 896 B -> unstaged 49 152 B, and the unstaged maximum
+  g = torch.Generator().manual_seed(seq + budget)
+  score = torch.rand(1, 1, seq, generator=g)
+  k = torch.randn(1, seq, 1, 64, generator=g).to(torch.bfloat16)
+  ref_cache, ref_idx = rm.kv_evict_topk_ref(score, k, k, budget)
+  cache, idx = att.kv_evict_topk(score.to(cuda_device), k.to(cuda_device), k.to(cuda_device), budget,
+                                 return_indices=True)
+  assert torch.equal(idx.cpu().long(), ref_idx) and torch.equal(cache.cpu(), ref_cache)
+
+
+def test_fp32_and_16bit_rows_alternate_at_a_long_sequence(cuda_device):
+  # each element width is its own kernel with its own shared-memory opt-in: a 16-bit call must not satisfy the
+  # fp32 kernel's set-up, nor the other way round
+  seq, budget = 20000, 64
+  g = torch.Generator().manual_seed(5)
+  score = torch.rand(1, 2, seq, generator=g)
+  sq = score * score / 7 + torch.rand(1, 2, seq, generator=g) * 1e-3
+  for dtype in (torch.bfloat16, torch.float32, torch.float16, torch.float32):
+    k = torch.randn(1, seq, 2, 64, generator=g).to(dtype)
+    ref_cache, ref_idx = rm.kv_evict_topk_ref(score, k, k, budget)
+    cache, idx = att.kv_evict_topk(score.to(cuda_device), k.to(cuda_device), k.to(cuda_device), budget,
+                                   return_indices=True)
+    assert torch.equal(idx.cpu().long(), ref_idx) and torch.equal(cache.cpu(), ref_cache)
+    ref_cache, ref_idx = rm.kv_evict_roco_ref(score, sq, k, k, 7, budget, 16)
+    cache, idx = att.kv_evict_roco(score.to(cuda_device), sq.to(cuda_device), k.to(cuda_device), k.to(cuda_device), 7,
+                                   budget, 16, return_indices=True)
+    assert torch.equal(idx.cpu().long(), ref_idx) and torch.equal(cache.cpu(), ref_cache)

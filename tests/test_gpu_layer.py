@@ -1,5 +1,7 @@
-"""Gemma-2-style decoder layer (config 5 shapes scaled down, and the attention part at full size) against the
-fp32 oracle restatement."""
+"""Gemma-2-style decoder layer (config 5's shapes scaled down) against the layer evaluated in fp32 end to end, at
+rtol = atol = 2e-2 on every element; the full-size layer is held to the same bar in tests/test_gpu_full_size.py.
+The reference has no code for this layer's options (grouped K/V heads, head_dim 256, sliding window, GeGLU): the
+oracle is a documented restatement of the reference's layer structure (models/gemma2.py:55-80)."""
 import pytest
 import torch
 
@@ -10,29 +12,33 @@ from oracle import reference_math as rm
 pytestmark = pytest.mark.gpu
 
 
-def assert_layer_close(got, ref):
-  """A chain of a dozen 16-bit ops: single-ulp flips of intermediate bf16 values (GEMM summation order) move a
-  small fraction of the outputs by a few ulps.  Bar: relative Frobenius error < 1e-2 (bf16 rounds at 2^-9 = 2e-3 per op), at most 2 % of the
-  elements outside rtol = atol = 2e-2, and no element off by more than 0.1 * (1 + |ref|)."""
-  diff = (got - ref).abs()
-  assert (diff.norm() / ref.norm()).item() < 1e-2
-  outside = (diff > 2e-2 + 2e-2 * ref.abs()).float().mean().item()
-  assert outside < 2e-2, outside
-  assert (diff / (1 + ref.abs())).max().item() < 0.1
-
-
-@pytest.mark.parametrize("S,window", [(384, 128), (600, 4096)])
-def test_layer_matches_oracle_small(cuda_device, S, window):
+@pytest.mark.parametrize("S,window", [(384, 128), (600, 4096), (1100, 300)])
+def test_layer_matches_fp32_oracle_small(cuda_device, S, window):
   cfg = L.Gemma2LayerConfig(hidden=512, heads=4, kv_heads=2, head_dim=256, window=window, intermediate=1024)
   w = L.init_weights(cfg, torch.bfloat16, cuda_device, seed=1, std=0.05)
   x = torch.randn(1, S, cfg.hidden, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
-  y = L.gemma2_layer(x.to(cuda_device), w, cfg)
-  ref = rm.gemma2_layer_ref(x, {k: t.cpu() for k, t in w.items()}, cfg.as_dict())
-  assert_layer_close(y.float().cpu(), ref)
+  y = L.gemma2_layer(x.to(cuda_device), w, cfg).float().cpu()
+  wc = {k: t.cpu() for k, t in w.items()}
+  ref = rm.gemma2_layer_ref_fp32(x, wc, cfg.as_dict())
+  torch.testing.assert_close(y, ref, rtol=2e-2, atol=2e-2)
+  # and against the 16-bit pipeline model (every op rounded to bf16 like the kernels round): closer in aggregate
+  model = rm.gemma2_layer_ref(x, wc, cfg.as_dict())
+  assert ((y - model).norm() / model.norm()).item() < 1e-2
 
 
-def test_config5_attention_full_size_slice(cuda_device):
-  # S 8192, head_dim 256, window 4096, softcap 50, GQA 2:1 -- one kv group (2 query heads) against the oracle
+def test_layer_input_is_not_modified_and_batches_are_independent(cuda_device):
+  cfg = L.Gemma2LayerConfig(hidden=512, heads=4, kv_heads=2, head_dim=256, window=200, intermediate=1024)
+  w = L.init_weights(cfg, torch.bfloat16, cuda_device, seed=3, std=0.05)
+  x = torch.randn(2, 300, cfg.hidden, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16).to(cuda_device)
+  keep = x.clone()
+  y = L.gemma2_layer(x, w, cfg)
+  assert torch.equal(x, keep)
+  y0 = L.gemma2_layer(x[:1].contiguous(), w, cfg)
+  torch.testing.assert_close(y[:1].float(), y0.float(), rtol=2e-2, atol=2e-2)   # GEMM tiling may differ with the batch
+
+
+def test_config5_attention_full_size_slice_on_cpu_oracle(cuda_device):
+  # S 8192, head_dim 256, window 4096, softcap 50, GQA 2:1 -- one kv group (2 query heads) against the CPU oracle
   S, D = 8192, 256
   g = torch.Generator().manual_seed(3)
   q = (torch.randn(1, S, 2, D, generator=g) * 2).to(torch.bfloat16)
@@ -43,12 +49,34 @@ def test_config5_attention_full_size_slice(cuda_device):
   torch.testing.assert_close(out.float().cpu(), ref, rtol=2e-2, atol=2e-2)
 
 
-def test_config5_layer_full_size_runs_and_is_finite(cuda_device):
-  cfg = L.Gemma2LayerConfig()
-  w = L.init_weights(cfg, torch.bfloat16, cuda_device, seed=4)
-  x = torch.randn(1, 8192, cfg.hidden, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).to(cuda_device)
-  y = L.gemma2_layer(x, w, cfg)
-  assert y.shape == x.shape and torch.isfinite(y.float()).all()
-  # first 256 tokens only depend on themselves (causal): compare that prefix with the oracle on the prefix
-  ref = rm.gemma2_layer_ref(x[:, :256].cpu(), {k: t.cpu() for k, t in w.items()}, cfg.as_dict())
-  assert_layer_close(y[:, :256].float().cpu(), ref)
+@pytest.mark.parametrize("variant", ["h2o", "roco", "kf"])
+def test_llama_score_layer_matches_fp32_flow(cuda_device, variant):
+  # the reference's per-layer flow (models/h2o.py:34-86): norm -> QKV -> RoPE -> attn_f -> eviction -> o_proj -> MLP,
+  # restated in fp32 from the oracle's pieces (the eviction step itself is held bit-exact in test_gpu_kv_evict.py)
+  cfg = L.LlamaLayerConfig(hidden=512, heads=4, kv_heads=4, intermediate=1024, cache_budget=96, roco_recent=32)
+  w = L.init_llama_weights(cfg, torch.bfloat16, cuda_device, seed=5, std=0.05)
+  B, S, H, D = 1, 640, cfg.heads, cfg.head_dim
+  x = torch.randn(B, S, cfg.hidden, generator=torch.Generator().manual_seed(6)).to(torch.bfloat16)
+  er = None
+  if variant == "kf":
+    er = -torch.log(torch.rand(B, H, S, S, generator=torch.Generator().manual_seed(7)).clamp_min(1e-7))
+  y, scores, cache = L.llama_score_layer(x.to(cuda_device), w, cfg, variant, er.to(cuda_device) if er is not None else None)
+  # fp32 restatement
+  wf = {k: t.float().cpu() for k, t in w.items()}
+  xf = x.float()
+  norm = lambda t, g: t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + cfg.eps) * g
+  qkv = norm(xf, wf["ln1"]) @ wf["qkv"].t()
+  q, k, v = qkv.split([H * D, H * D, H * D], dim=-1)
+  pos = torch.arange(S, dtype=torch.int32)
+  qr, kr = rm.rotary_online_ref(pos, q.reshape(S, H * D), k.reshape(S, H * D), D, cfg.rope_theta)
+  want = {"h2o": ("out", "colsum"), "roco": ("out", "colsum", "colsum_sq"), "kf": ("out", "kf")}[variant]
+  ref = rm.attention_ref(qr.view(B, S, H, D), kr.view(B, S, H, D), v.reshape(B, S, H, D), exp_rand=er, tau=cfg.tau,
+                         want=want)
+  x1 = xf + ref["out"].reshape(B, S, H * D) @ wf["o"].t()
+  gu = norm(x1, wf["ln2"]) @ wf["gate_up"].t()
+  d = gu.shape[-1] // 2
+  yr = x1 + (torch.nn.functional.silu(gu[..., :d]) * gu[..., d:]) @ wf["down"].t()
+  torch.testing.assert_close(y.float().cpu(), yr, rtol=2e-2, atol=2e-2)
+  # scores: the layer's q, k are bf16-rounded projections, the restatement's are fp32 -> looser than the kernel bar
+  torch.testing.assert_close(scores[0].cpu(), ref[want[1]], rtol=5e-2, atol=1e-3)
+  assert cache.shape == (B, 2, cfg.cache_budget + (cfg.roco_recent if variant == "roco" else 0), H, D)
