@@ -54,9 +54,14 @@ struct SweepParams {
   float scale_log2, cap_in, cap_out, inv_tau;
 };
 
-template <int MODE_, int BX_, int STAGES_>
+// CWG_ = compute warpgroups per CTA.  With two, warpgroup g reduces columns [g * BX/2, (g+1) * BX/2) of every
+// product tile (both cover all 128 TMEM lanes, i.e. all stationary rows) and the two partial results of a row are
+// added once at the end: twice the warps per scheduler hide the TMEM-load, shared-memory and special-function
+// latencies of the element loop, which with one warp per scheduler and CTA bound the sweep (measured: special-
+// function unit 55 % busy, issue slots 37 %, moving exponentials to the FMA pipe changed nothing).
+template <int MODE_, int BX_, int STAGES_, int CWG_ = 1>
 struct SweepCfg {
-  static constexpr int MODE = MODE_, BX = BX_, STAGES = STAGES_;
+  static constexpr int MODE = MODE_, BX = BX_, STAGES = STAGES_, CWG = CWG_;
   static constexpr int D = 128, BM = 128;
   static constexpr bool NOISE = MODE != SWEEP_COLSUM;
   static constexpr bool LSE_IN = MODE != SWEEP_KF_ROWLSE;
@@ -73,7 +78,10 @@ struct SweepCfg {
   static constexpr int N_STAGE_BYTES = NOISE_BYTES + LSE_BYTES;       // auxiliary ring read by the compute warps
   static constexpr int N_STAGE_STRIDE = (N_STAGE_BYTES + 1023) / 1024 * 1024;
   static constexpr int TMEM_COLS = A_TMEM ? 256 : 2 * BX;               // two product tiles (+ the stationary tile)
-  static constexpr int THREADS = 6 * 32;
+  static constexpr int COMPUTE_WARPS = 4 * CWG;
+  static constexpr int THREADS = (COMPUTE_WARPS + 2) * 32;   // + TMA producer warp + MMA issuer warp
+  static constexpr int CTAS_PER_SM = CWG == 2 ? 2 : 1;       // launch bound (registers): two 320-thread CTAs share an SM
+  static_assert(CWG == 1 || (CWG == 2 && BX == 128 && !A_TMEM), "two compute warpgroups: 128-wide blocks only");
   static constexpr int BAR_A_FULL = 0;
   static constexpr int BAR_X_FULL = 1;
   static constexpr int BAR_X_EMPTY = BAR_X_FULL + STAGES;
@@ -82,8 +90,11 @@ struct SweepCfg {
   static constexpr int BAR_T_FULL = BAR_N_EMPTY + STAGES;   // [2]
   static constexpr int BAR_T_EMPTY = BAR_T_FULL + 2;        // [2]
   static constexpr int BAR_DRAIN = BAR_T_EMPTY + 2;
-  static constexpr int NUM_BARS = BAR_DRAIN + 1;
-  static constexpr int SMEM_BYTES = A_BYTES + STAGES * X_STAGE_BYTES + STAGES * N_STAGE_STRIDE + NUM_BARS * 8 + 16 + 1024;
+  static constexpr int BAR_COMBINE = BAR_DRAIN + 1;         // second compute warpgroup's sums are in shared memory
+  static constexpr int NUM_BARS = BAR_COMBINE + 1;
+  static constexpr int COMBINE_BYTES = CWG == 2 ? 2 * 128 * 4 : 0;   // second warpgroup's partial sums
+  static constexpr int SMEM_BYTES = A_BYTES + STAGES * X_STAGE_BYTES + STAGES * N_STAGE_STRIDE + COMBINE_BYTES +
+                                    NUM_BARS * 8 + 16 + 1024;
 };
 
 template <class Cfg>
@@ -91,6 +102,7 @@ struct SweepCtx {
   uint8_t* sA;
   uint8_t* sX;
   uint8_t* sN;
+  float* sCombine;   // [2][128], two compute warpgroups only
   uint64_t* bars;
   volatile int* abort_flag;
   uint32_t tmem_base;
@@ -331,18 +343,22 @@ __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, con
     const bool need_mask = (p.causal && (c.a0 + 127 - p.delta > i0)) || (i0 + BX > p.q_len) ||
                            (c.a0 + 128 > p.kv_len) ||
                            (p.causal && p.window > 0 && (c.a0 + p.window - 1 - p.delta < i0 + BX - 1));
-    // the TMEM load of chunk ch+1 is in flight while chunk ch is being reduced
+    // the TMEM load of chunk ch+1 is in flight while chunk ch is being reduced; with two compute warpgroups
+    // each takes its own half of the tile's columns
+    constexpr int NCH = BX / 32 / Cfg::CWG;
+    const int ch0 = Cfg::CWG == 2 ? (int)(threadIdx.x >> 7) * NCH : 0;
     uint32_t sr[2][32];
-    tmem_ld32(lane_addr + tb * BX, sr[0]);
+    tmem_ld32(lane_addr + tb * BX + ch0 * 32, sr[0]);
 #pragma unroll
-    for (int ch = 0; ch < BX / 32; ++ch) {
+    for (int cc = 0; cc < NCH; ++cc) {
+      const int ch = ch0 + cc;
       tmem_ld_wait();
-      if (ch + 1 < BX / 32) tmem_ld32(lane_addr + tb * BX + (ch + 1) * 32, sr[(ch + 1) & 1]);
+      if (cc + 1 < NCH) tmem_ld32(lane_addr + tb * BX + (ch + 1) * 32, sr[(cc + 1) & 1]);
       if (need_mask)
-        chunk_body(std::true_type{}, sr[ch & 1], ch, lse_s, noise_col, lo_c, hi_c, (float)(i0 + 1));
+        chunk_body(std::true_type{}, sr[cc & 1], ch, lse_s, noise_col, lo_c, hi_c, (float)(i0 + 1));
       else
-        chunk_body(std::false_type{}, sr[ch & 1], ch, lse_s, noise_col, lo_c, hi_c, (float)(i0 + 1));
-      if (tl_on && ch < 4) B200_TL(tl_base + 3 + ch);
+        chunk_body(std::false_type{}, sr[cc & 1], ch, lse_s, noise_col, lo_c, hi_c, (float)(i0 + 1));
+      if (tl_on && cc < 4) B200_TL(tl_base + 3 + cc);
     }
     // this TMEM buffer and this auxiliary stage may be refilled
     tc_fence_before();
@@ -353,11 +369,25 @@ __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, con
     }
     if (tl_on) B200_TL(tl_base + 7);
   }
-  const float acc0 = acc2.x, acc1 = acc2.y, sq0 = sq2.x, sq1 = sq2.y;
+  float acc = acc2.x + acc2.y;
+  float aux = AUX == AUX_CORM ? fmaxf(sq2.x, sq2.y) : sq2.x + sq2.y;
+  if constexpr (Cfg::CWG == 2) {
+    // the second warpgroup hands its sums over through shared memory; the first adds them in a fixed order
+    const int r = threadIdx.x & 127;
+    if (threadIdx.x >= 128) {
+      c.sCombine[r] = acc;
+      c.sCombine[128 + r] = aux;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&c.bars[Cfg::BAR_COMBINE]);   // count 4: one arrival per warp of the second group
+      return;
+    }
+    if (!mbar_wait(&c.bars[Cfg::BAR_COMBINE], 0, c.abort_flag, WAIT_T_FULL)) return;
+    acc += c.sCombine[r];
+    aux = AUX == AUX_CORM ? fmaxf(aux, c.sCombine[128 + r]) : aux + c.sCombine[128 + r];
+  }
   const int64_t off = ((int64_t)c.bh * p.n_chunks + chunk) * p.kv_pad + key;
-  p.partial[off] = acc0 + acc1;
-  if constexpr (AUX == AUX_SQUARES) p.partial_sq[off] = sq0 + sq1;
-  if constexpr (AUX == AUX_CORM) p.partial_sq[off] = fmaxf(sq0, sq1);
+  p.partial[off] = acc;
+  if constexpr (AUX != AUX_NONE) p.partial_sq[off] = aux;
 }
 
 
@@ -516,11 +546,12 @@ __device__ __forceinline__ void sweep_compute_rowlse(const SweepCtx<Cfg>& c, con
 // tile that meets the most streamed blocks first, z = chunk of streamed blocks.  Blocks are dispatched x-fastest,
 // so the launch walks ALL units' heaviest tiles first and ends on the lightest ones (longest-processing-time-first
 // over the whole launch, not per head): under a causal mask a tile's work ranges from one block to all of them.
-template <int MODE, int BX, int STAGES, bool BF16, bool SOFTCAP, int AUX, bool GROUPED = false>
-__global__ void __launch_bounds__(192, 1)
+template <int MODE, int BX, int STAGES, bool BF16, bool SOFTCAP, int AUX, bool GROUPED = false, int CWG = 1>
+__global__ void __launch_bounds__((SweepCfg<MODE, BX, STAGES, CWG>::THREADS), (SweepCfg<MODE, BX, STAGES, CWG>::CTAS_PER_SM))
 attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_x,
                   const __grid_constant__ CUtensorMap tm_n, const SweepParams p) {
-  using Cfg = SweepCfg<MODE, BX, STAGES>;
+  using Cfg = SweepCfg<MODE, BX, STAGES, CWG>;
+  constexpr int CW = Cfg::COMPUTE_WARPS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   // A launch that follows an expired wait on this device drains immediately (the status word stays
@@ -535,7 +566,8 @@ attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   c.sA = smem;
   c.sX = c.sA + Cfg::A_BYTES;
   c.sN = c.sX + STAGES * Cfg::X_STAGE_BYTES;
-  c.bars = reinterpret_cast<uint64_t*>(c.sN + STAGES * Cfg::N_STAGE_STRIDE);
+  c.sCombine = reinterpret_cast<float*>(c.sN + STAGES * Cfg::N_STAGE_STRIDE);
+  c.bars = reinterpret_cast<uint64_t*>(c.sN + STAGES * Cfg::N_STAGE_STRIDE + Cfg::COMBINE_BYTES);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(c.bars + Cfg::NUM_BARS);
   c.abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -576,14 +608,16 @@ attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   if (threadIdx.x == 0) {
 #pragma unroll
     for (int i = 0; i < Cfg::NUM_BARS; ++i) {
+      // arrivals per phase: every compute warp releases a product buffer / an auxiliary stage
       const bool warp_count = (i >= Cfg::BAR_N_EMPTY && i < Cfg::BAR_N_EMPTY + STAGES) ||
                               (i >= Cfg::BAR_T_EMPTY && i < Cfg::BAR_T_EMPTY + 2);
-      mbar_init(&c.bars[i], (warp_count || (Cfg::A_TMEM && i == Cfg::BAR_A_FULL)) ? 4u : 1u);
+      const bool four = (Cfg::A_TMEM && i == Cfg::BAR_A_FULL) || i == Cfg::BAR_COMBINE;
+      mbar_init(&c.bars[i], warp_count ? (uint32_t)Cfg::COMPUTE_WARPS : four ? 4u : 1u);
     }
     *c.abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == CW && lane == 0) {
     tma_prefetch_desc(&tm_a);
     tma_prefetch_desc(&tm_x);
     if constexpr (Cfg::NOISE) tma_prefetch_desc(&tm_n);
@@ -597,7 +631,7 @@ attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   tc_fence_after();
   c.tmem_base = *tmem_slot;
 
-  if (warp < 4) {
+  if (warp < CW) {
     if constexpr (Cfg::A_TMEM) {
       // thread r copies row r of the stationary tile (256 contiguous bytes) from global memory into TMEM lane r;
       // a 32-bit TMEM column holds two consecutive 16-bit elements, which is the order they have in memory
@@ -630,7 +664,7 @@ attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       sweep_compute_colsum_grouped<Cfg, SOFTCAP, AUX>(c, p, chunk);
     else
       sweep_compute_colsum<Cfg, SOFTCAP, AUX>(c, p, chunk);
-  } else if (warp == 4) {
+  } else if (warp == CW) {
     if (lane == 0) sweep_producer<Cfg, GROUPED>(c, p, &tm_a, &tm_x, &tm_n);
   } else {
     sweep_mma<Cfg, BF16>(c, (c.blk_hi - c.blk_lo) * (GROUPED ? p.kv_group : 1));
@@ -678,9 +712,15 @@ constexpr int kSweepChunkBlocks = B200_SWEEP_CHUNK;
 #ifndef B200_COLSUM_STAGES
 #define B200_COLSUM_STAGES 2
 #endif
+// KeyFormer sweeps: two ring stages of 8 KB (streamed operand) + 32 KB (noise) keep a CTA at 83 KB of shared memory, so
+// that two CTAs share an SM (measured at config 4: 430 -> 322 us against three stages and one CTA per SM)
 #ifndef B200_KF_STAGES
-#define B200_KF_STAGES 3
-#endif   // streamed blocks per CTA in the column-sum sweeps
+#define B200_KF_STAGES 2
+#endif
+// compute warpgroups of the plain column-sum sweep (see SweepCfg)
+#ifndef B200_COLSUM_CWG
+#define B200_COLSUM_CWG (B200_COLSUM_BX == 128 ? 2 : 1)
+#endif
 
 struct ScoreWorkspace {
   int lse_stride, kv_pad, n_chunks_colsum, n_chunks_kf;
@@ -711,11 +751,11 @@ inline int64_t score_workspace_bytes(int batch, int q_len, int kv_len, int heads
 }
 
 // n_chunks chunks of streamed blocks x n_tiles stationary tiles x (batch x heads) units -- (batch x K/V heads) when GROUPED
-template <int MODE, int BX, int STAGES, bool BF16, bool SOFTCAP, int AUX, bool GROUPED = false>
+template <int MODE, int BX, int STAGES, bool BF16, bool SOFTCAP, int AUX, bool GROUPED = false, int CWG = 1>
 int launch_sweep(const CUtensorMap& ta, const CUtensorMap& tx, const CUtensorMap& tn, const SweepParams& p,
                  int n_chunks, int n_tiles, cudaStream_t stream) {
-  using Cfg = SweepCfg<MODE, BX, STAGES>;
-  auto kern = attn_sweep_kernel<MODE, BX, STAGES, BF16, SOFTCAP, AUX, GROUPED>;
+  using Cfg = SweepCfg<MODE, BX, STAGES, CWG>;
+  auto kern = attn_sweep_kernel<MODE, BX, STAGES, BF16, SOFTCAP, AUX, GROUPED, CWG>;
   static thread_local int configured_dev = -1;
   int dev = 0;
   B200_CUDA_TRY(cudaGetDevice(&dev));
@@ -856,8 +896,9 @@ inline int attn_score_impl(const void* q, const void* k, const void* v, void* ou
     return B200_OK;
   }
 
-#define B200_SWEEP0(BF, CAP, AUXV) \
-  launch_sweep<SWEEP_COLSUM, B200_COLSUM_BX, B200_COLSUM_STAGES, BF, CAP, AUXV>(ta, tx, tn, p, p.n_chunks, gy, stream)
+#define B200_SWEEP0(BF, CAP, AUXV)                                                                      \
+  launch_sweep<SWEEP_COLSUM, B200_COLSUM_BX, B200_COLSUM_STAGES, BF, CAP, AUXV, false, B200_COLSUM_CWG>( \
+      ta, tx, tn, p, p.n_chunks, gy, stream)
   if (corm_flags != nullptr)
     rc = bf16 ? B200_SWEEP0(true, false, AUX_CORM) : B200_SWEEP0(false, false, AUX_CORM);
   else if (bf16)
