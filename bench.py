@@ -19,7 +19,8 @@ Further records on the same line:
   sub              (N = 1) one record per other configuration: config 3 (H2O, RoCo), config 4 (KeyFormer), config 5
                    (attention, whole layer), the reference's Llama-shaped H2O layer, the five bandwidth ops, the
                    reference's default shape (batch 1, 32 heads, seq 4096, fp16) and the seq-length sweep:
-                   median and min over --sub-iters launches, each timed alone with CUDA events after an L2 flush
+                   median and min per launch over batches of launches (CUDA events around a batch) that rotate over
+                   buffer sets whose total footprint is several times L2
 
 --impl reference times the CPU port alone (all host threads) and prints the same line shape.
 FLOPs follow the reference's own formula 4*B*H*S*S*D/2 (run_kernel.py:24).
@@ -231,22 +232,37 @@ def run_reference_arm(args, rank, world):
 # ----------------------------------------------------------------------------------------------------------
 # GPU helpers
 # ----------------------------------------------------------------------------------------------------------
-def time_op(fn, iters, warmup, flush=None):
-  """Median and minimum time (microseconds) of `fn()` over `iters` launches, each bracketed by its own pair of CUDA
-  events on the current stream; `flush` (a buffer larger than L2) is rewritten before every timed launch, outside
-  the event pair."""
-  for _ in range(warmup):
-    fn()
-  pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+L2_BYTES = 126 << 20
+
+
+def time_op(fns, iters, warmup):
+  """Median and minimum time per launch (microseconds).  `fns` are closures of the SAME operation on different buffer
+  sets whose total footprint exceeds L2 several times over (or a single closure whose own inputs do): a timed batch
+  walks the sets round robin, at least four launches per batch, between one pair of CUDA events on the current
+  stream, so that a launch neither finds its inputs in L2 nor carries the ~5 us gap of an event pair of its own.
+  At least `iters` launches are timed in all."""
+  if callable(fns):
+    fns = [fns]
+  per_batch = max(len(fns), 4)
+  for i in range(max(warmup, len(fns))):
+    fns[i % len(fns)]()
+  batches = max(10, -(-iters // per_batch))
+  pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(batches)]
+  k = 0
   for e0, e1 in pairs:
-    if flush is not None:
-      flush.add_(1)
     e0.record()
-    fn()
+    for _ in range(per_batch):
+      fns[k % len(fns)]()
+      k += 1
     e1.record()
   torch.cuda.synchronize()
-  ts = sorted(e0.elapsed_time(e1) * 1e3 for e0, e1 in pairs)
+  ts = sorted(e0.elapsed_time(e1) * 1e3 / per_batch for e0, e1 in pairs)
   return ts[len(ts) // 2], ts[0]
+
+
+def buffer_sets(footprint_bytes, cap=12):
+  """How many independent buffer sets of `footprint_bytes` make a rotation that outgrows L2 (4 x L2, at most `cap`)."""
+  return int(max(1, min(cap, -(-4 * L2_BYTES // max(1, footprint_bytes)))))
 
 
 def sub_records(dev, peaks, iters, warmup):
@@ -255,113 +271,120 @@ def sub_records(dev, peaks, iters, warmup):
   from deepgengraph_b200 import layer as L
   from deepgengraph_b200 import native_ops as ops
   recs = []
-  flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)   # 256 MiB > the 126 MB L2
   gen = torch.Generator(device=dev).manual_seed(7)
   peak_tf, peak_bw = peaks["tflops"], peaks["hbm_gbs"]
 
   def randn(*shape, dtype=torch.bfloat16, scale=1.0):
     return (torch.randn(*shape, generator=gen, device=dev, dtype=torch.float32) * scale).to(dtype)
 
-  def tensor_rec(name, workload, fn, flops, extra=None):
-    med, mn = time_op(fn, iters, warmup, flush)
-    r = {"name": name, "workload": workload, "us_median": med, "us_min": mn, "tflops": flops / med / 1e6,
-         "bound": "tensor", "frac_of_measured_peak": flops / med / 1e6 / peak_tf, "iters": iters}
+  def record(name, workload, fns, bound, work, extra=None):
+    """work = algorithmic flops (tensor) or bytes (hbm) per launch."""
+    n_sets = len(fns) if isinstance(fns, list) else 1
+    med, mn = time_op(fns, iters, warmup)
+    r = {"name": name, "workload": workload, "us_median": med, "us_min": mn, "bound": bound, "buffer_sets": n_sets}
+    if bound == "tensor":
+      r.update(tflops=work / med / 1e6, frac_of_measured_peak=work / med / 1e6 / peak_tf)
+    else:
+      r.update(gbs=work / med / 1e3, algorithmic_bytes=work, frac_of_measured_peak=work / med / 1e3 / peak_bw)
     if extra:
       r.update(extra)
     recs.append(r)
     return r
 
-  def hbm_rec(name, workload, fn, nbytes, extra=None):
-    med, mn = time_op(fn, iters, warmup, flush)
-    r = {"name": name, "workload": workload, "us_median": med, "us_min": mn, "gbs": nbytes / med / 1e3,
-         "bound": "hbm", "algorithmic_bytes": nbytes, "frac_of_measured_peak": nbytes / med / 1e3 / peak_bw,
-         "iters": iters}
-    if extra:
-      r.update(extra)
-    recs.append(r)
-    return r
+  def qkv_sets(b, s, h, hk, d, dtype=torch.bfloat16, q_scale=1.0):
+    n = buffer_sets((2 * b * s * h * d + 2 * b * s * hk * d) * 2)
+    return [(randn(b, s, h, d, dtype=dtype, scale=q_scale), randn(b, s, hk, d, dtype=dtype), randn(b, s, hk, d, dtype=dtype))
+            for _ in range(n)]
+
+  def over(sets, f):
+    return [(lambda t=t: f(*t)) for t in sets]
 
   # ---- config 3: H2O / RoCo (attention + per-key column sums) ----
   b3, h3, s3 = 2, 32, 4096
-  q, k, v = (randn(b3, s3, h3, D) for _ in range(3))
+  sets = qkv_sets(b3, s3, h3, h3, D)
   f3 = causal_flops(b3, h3, s3, D)
   w3 = "config3: B2 H32 S4096 D128 bf16 causal"
-  tensor_rec("config3_h2o", w3 + ", out + sum_i p", lambda: att.attn_score_fwd(q, k, v), f3,
-             {"credited_flops": "attention only (the second QK^T of the sweep is overhead)"})
-  tensor_rec("config3_roco", w3 + ", out + sum_i p + sum_i p^2", lambda: att.attn_score_fwd(q, k, v, want_sq=True), f3)
-  tensor_rec("config3_forward_only", w3 + ", out only", lambda: att.attn_fwd(q, k, v), f3)
-  score = att.attn_score_fwd(q, k, v)[1]
-  hbm_rec("config3_kv_evict_topk", w3 + ", budget 512: topk -> sort -> gather",
-          lambda: att.kv_evict_topk(score, k, v, 512), score.numel() * 4 + 4 * b3 * 512 * h3 * D * 2)
+  record("config3_h2o", w3 + ", out + sum_i p", over(sets, lambda q, k, v: att.attn_score_fwd(q, k, v)), "tensor", f3,
+         {"credited_flops": "attention only (the second QK^T of the sweep is overhead)"})
+  record("config3_roco", w3 + ", out + sum_i p + sum_i p^2",
+         over(sets, lambda q, k, v: att.attn_score_fwd(q, k, v, want_sq=True)), "tensor", f3)
+  record("config3_forward_only", w3 + ", out only", over(sets, lambda q, k, v: att.attn_fwd(q, k, v)), "tensor", f3)
+  record("config2_shape_softcap50", "B2 H32 S4096 D128 bf16 causal, soft-cap 50",
+         over(sets, lambda q, k, v: att.attn_fwd(q, k, v, softcap=50.0)), "tensor", f3)
+  scores = [att.attn_score_fwd(*t)[1] for t in sets]
+  record("config3_kv_evict_topk", w3 + ", budget 512: topk -> sort -> gather",
+         [(lambda t=t, sc=sc: att.kv_evict_topk(sc, t[1], t[2], 512)) for t, sc in zip(sets, scores)], "hbm",
+         scores[0].numel() * 4 + 4 * b3 * 512 * h3 * D * 2)
+  del sets, scores
+
   # the reference's default shape (run_kernel.py:20-24; the workload of its Fig. 14): batch 1, 32 heads, seq 4096, fp16
-  qh, kh, vh = (t[:1].to(torch.float16).contiguous() for t in (q, k, v))
-  tensor_rec("reference_default_attn_fp16", "B1 H32 S4096 D128 fp16 causal (run_kernel.py defaults)",
-             lambda: att.attn_fwd(qh, kh, vh), causal_flops(1, 32, 4096, D),
-             {"published_a100_ms": {"FlashTensor": 0.929, "FlashAttention-2": 0.980, "TensorRT": 2.01}})
-  tensor_rec("reference_default_gemma2_fp16", "B1 H32 S4096 D128 fp16 causal, soft-cap 50",
-             lambda: att.attn_fwd(qh, kh, vh, softcap=50.0), causal_flops(1, 32, 4096, D),
-             {"published_a100_ms": {"FlashTensor": 0.937, "FlashAttention-2": 1.314, "TensorRT": 4.27}})
-  tensor_rec("config2_softcap50", "config2 shape (B2 of it) with soft-cap 50", lambda: att.attn_fwd(q, k, v, softcap=50.0), f3)
-  del qh, kh, vh, score
+  sets = qkv_sets(1, 4096, 32, 32, D, dtype=torch.float16)
+  record("reference_default_attn_fp16", "B1 H32 S4096 D128 fp16 causal (run_kernel.py defaults)",
+         over(sets, lambda q, k, v: att.attn_fwd(q, k, v)), "tensor", causal_flops(1, 32, 4096, D),
+         {"published_a100_ms": {"FlashTensor": 0.929, "FlashAttention-2": 0.980, "TensorRT": 2.01}})
+  record("reference_default_gemma2_fp16", "B1 H32 S4096 D128 fp16 causal, soft-cap 50",
+         over(sets, lambda q, k, v: att.attn_fwd(q, k, v, softcap=50.0)), "tensor", causal_flops(1, 32, 4096, D),
+         {"published_a100_ms": {"FlashTensor": 0.937, "FlashAttention-2": 1.314, "TensorRT": 4.27}})
+  del sets
 
   # ---- seq-length sweep at batch 1, 32 heads (the reference's fig13/run.sh:30) ----
   for s in (1024, 2048, 4096, 8192):
-    qs, ks, vs = (randn(1, s, 32, D) for _ in range(3))
-    tensor_rec(f"sweep_attn_s{s}", f"B1 H32 S{s} D128 bf16 causal", lambda: att.attn_fwd(qs, ks, vs),
-               causal_flops(1, 32, s, D))
-    tensor_rec(f"sweep_h2o_s{s}", f"B1 H32 S{s} D128 bf16 causal, out + sum_i p", lambda: att.attn_score_fwd(qs, ks, vs),
-               causal_flops(1, 32, s, D))
-  del qs, ks, vs, q, k, v
+    sets = qkv_sets(1, s, 32, 32, D)
+    record(f"sweep_attn_s{s}", f"B1 H32 S{s} D128 bf16 causal", over(sets, lambda q, k, v: att.attn_fwd(q, k, v)),
+           "tensor", causal_flops(1, 32, s, D))
+    record(f"sweep_h2o_s{s}", f"B1 H32 S{s} D128 bf16 causal, out + sum_i p",
+           over(sets, lambda q, k, v: att.attn_score_fwd(q, k, v)), "tensor", causal_flops(1, 32, s, D))
+    del sets
 
   # ---- config 4: KeyFormer with the [B, H, S, S] fp32 noise tensor as an input (HBM-bound) ----
   b4, h4, s4 = 2, 32, 2048
   q, k, v = (randn(b4, s4, h4, D) for _ in range(3))
   exp_rand = -torch.log(torch.rand(b4, h4, s4, s4, generator=gen, device=dev).clamp_min_(1e-7))
   bytes4 = exp_rand.numel() * 4 + 4 * q.numel() * 2 + b4 * h4 * s4 * 4
-  hbm_rec("config4_keyformer", "config4: B2 H32 S2048 D128 bf16 causal, tau 1.0, Gumbel noise tensor input (1.07 GB)",
-          lambda: att.attn_kf_fwd(q, k, v, exp_rand, tau=1.0), bytes4,
-          {"tflops_credited": causal_flops(b4, h4, s4, D) / 1e12, "note": "noise counted once in the algorithmic bytes"})
+  record("config4_keyformer", "config4: B2 H32 S2048 D128 bf16 causal, tau 1.0, Gumbel noise tensor input (1.07 GB)",
+         lambda: att.attn_kf_fwd(q, k, v, exp_rand, tau=1.0), "hbm", bytes4,
+         {"tflops_credited": causal_flops(b4, h4, s4, D) / 1e12, "note": "noise counted once in the algorithmic bytes"})
   del exp_rand, q, k, v
 
   # ---- config 5: attention, whole Gemma-2-style layer, bandwidth ops ----
   cfg = L.Gemma2LayerConfig()
   s5, T = 8192, 8192
-  q = randn(1, s5, cfg.heads, cfg.head_dim, scale=2.0)
-  k, v = (randn(1, s5, cfg.kv_heads, cfg.head_dim) for _ in range(2))
+  sets = qkv_sets(1, s5, cfg.heads, cfg.kv_heads, cfg.head_dim, q_scale=2.0)
   f5 = window_flops(cfg.heads, s5, cfg.head_dim, cfg.window)
-  tensor_rec("config5_attention", "config5: B1 S8192 16q/8kv heads D256 window 4096 soft-cap 50 bf16",
-             lambda: att.attn_fwd(q, k, v, window=cfg.window, softcap=cfg.softcap), f5)
-  del q, k, v
+  record("config5_attention", "config5: B1 S8192 16q/8kv heads D256 window 4096 soft-cap 50 bf16",
+         over(sets, lambda q, k, v: att.attn_fwd(q, k, v, window=cfg.window, softcap=cfg.softcap)), "tensor", f5)
+  del sets
   w = L.init_weights(cfg, torch.bfloat16, dev, seed=0)
   x = randn(1, s5, cfg.hidden)
   qkv_out = (cfg.heads + 2 * cfg.kv_heads) * cfg.head_dim
   gemm_flops = 2.0 * T * (cfg.hidden * qkv_out + cfg.heads * cfg.head_dim * cfg.hidden +
                           cfg.hidden * 2 * cfg.intermediate + cfg.intermediate * cfg.hidden)
-  tensor_rec("config5_layer", "config5: Gemma-2-style decoder layer, hidden 3584, GeGLU 14336 (4 cuBLAS GEMMs + this library's ops)",
-             lambda: L.gemma2_layer(x, w, cfg), gemm_flops + f5, {"gemm_tflop": gemm_flops / 1e12})
-  del w
-  sz = 2
-  hid = cfg.hidden
-  xin, out = randn(T, hid), torch.empty(T, hid, dtype=torch.bfloat16, device=dev)
+  record("config5_layer", "config5: Gemma-2-style decoder layer, hidden 3584, GeGLU 14336 (4 cuBLAS GEMMs + this library's ops)",
+         lambda: L.gemma2_layer(x, w, cfg), "tensor", gemm_flops + f5, {"gemm_tflop": gemm_flops / 1e12})
+  del w, x
+  sz, hid = 2, cfg.hidden
   wn = (1 + 0.02 * randn(hid).float()).to(torch.bfloat16)
-  hbm_rec("rms_norm", f"[{T}, {hid}] bf16", lambda: ops.rms_norm(out, xin, wn, cfg.eps), 2 * T * hid * sz + hid * sz)
-  res = randn(T, hid)
-  hbm_rec("fused_add_rms_norm", f"[{T}, {hid}] bf16, in place", lambda: ops.fused_add_rms_norm(xin, res, wn, cfg.eps),
-          4 * T * hid * sz)
-  del xin, out, res
-  gu = randn(T, 2 * cfg.intermediate)
-  act = torch.empty(T, cfg.intermediate, dtype=torch.bfloat16, device=dev)
-  hbm_rec("gelu_tanh_and_mul", f"[{T}, 2x{cfg.intermediate}] bf16", lambda: ops.gelu_tanh_and_mul(act, gu),
-          3 * T * cfg.intermediate * sz)
-  hbm_rec("silu_and_mul", f"[{T}, 2x{cfg.intermediate}] bf16", lambda: ops.silu_and_mul(act, gu),
-          3 * T * cfg.intermediate * sz)
-  del gu, act
-  qr, kr = randn(T, cfg.heads * cfg.head_dim), randn(T, cfg.kv_heads * cfg.head_dim)
+  n = buffer_sets(2 * T * hid * sz)
+  xs = [(randn(T, hid), torch.empty(T, hid, dtype=torch.bfloat16, device=dev)) for _ in range(n)]
+  record("rms_norm", f"[{T}, {hid}] bf16", [(lambda t=t: ops.rms_norm(t[1], t[0], wn, cfg.eps)) for t in xs], "hbm",
+         2 * T * hid * sz + hid * sz)
+  record("fused_add_rms_norm", f"[{T}, {hid}] bf16, in place",
+         [(lambda t=t: ops.fused_add_rms_norm(t[0], t[1], wn, cfg.eps)) for t in xs], "hbm", 4 * T * hid * sz)
+  del xs
+  n = buffer_sets(3 * T * cfg.intermediate * sz, cap=4)
+  gs = [(randn(T, 2 * cfg.intermediate), torch.empty(T, cfg.intermediate, dtype=torch.bfloat16, device=dev)) for _ in range(n)]
+  record("gelu_tanh_and_mul", f"[{T}, 2x{cfg.intermediate}] bf16", [(lambda t=t: ops.gelu_tanh_and_mul(t[1], t[0])) for t in gs],
+         "hbm", 3 * T * cfg.intermediate * sz)
+  record("silu_and_mul", f"[{T}, 2x{cfg.intermediate}] bf16", [(lambda t=t: ops.silu_and_mul(t[1], t[0])) for t in gs],
+         "hbm", 3 * T * cfg.intermediate * sz)
+  del gs
   pos = torch.arange(T, dtype=torch.int32, device=dev)
-  hbm_rec("rotary_embedding_online", f"q [{T}, {cfg.heads}x{cfg.head_dim}], k [{T}, {cfg.kv_heads}x{cfg.head_dim}] bf16",
-          lambda: ops.rotary_embedding_online(pos, qr, kr, cfg.head_dim, cfg.rope_theta),
-          2 * T * (cfg.heads + cfg.kv_heads) * cfg.head_dim * sz + 4 * T)
-  del qr, kr
+  n = buffer_sets(2 * T * (cfg.heads + cfg.kv_heads) * cfg.head_dim * sz)
+  rs = [(randn(T, cfg.heads * cfg.head_dim), randn(T, cfg.kv_heads * cfg.head_dim)) for _ in range(n)]
+  record("rotary_embedding_online", f"q [{T}, {cfg.heads}x{cfg.head_dim}], k [{T}, {cfg.kv_heads}x{cfg.head_dim}] bf16",
+         [(lambda t=t: ops.rotary_embedding_online(pos, t[0], t[1], cfg.head_dim, cfg.rope_theta)) for t in rs], "hbm",
+         2 * T * (cfg.heads + cfg.kv_heads) * cfg.head_dim * sz + 4 * T)
+  del rs
 
   # ---- the reference's Llama-shaped layer with a score variant and the eviction fused in (models/h2o.py:34-86),
   #      random weights as in run_e2e.py:48-66: hidden 4096, 32 heads, intermediate 11008, fp16, seq 4096 ----
@@ -372,9 +395,9 @@ def sub_records(dev, peaks, iters, warmup):
   lg = 2.0 * sl * (lc.hidden * 3 * lc.hidden + lc.hidden * lc.hidden + lc.hidden * 2 * lc.intermediate +
                    lc.intermediate * lc.hidden)
   for variant in ("h2o", "roco"):
-    tensor_rec(f"llama_layer_{variant}", f"Llama-7B-shaped layer fp16, seq 4096, {variant} scores + KV eviction to 512 keys",
-               lambda: L.llama_score_layer(xl, lw, lc, variant), lg + causal_flops(1, lc.heads, sl, lc.head_dim),
-               {"gemm_tflop": lg / 1e12})
+    record(f"llama_layer_{variant}", f"Llama-7B-shaped layer fp16, seq 4096, {variant} scores + KV eviction to 512 keys",
+           lambda: L.llama_score_layer(xl, lw, lc, variant), "tensor", lg + causal_flops(1, lc.heads, sl, lc.head_dim),
+           {"gemm_tflop": lg / 1e12})
   return recs
 
 
@@ -588,7 +611,7 @@ def main():
     del q, k, v, out
     torch.cuda.empty_cache()
     if world == 1 and not args.no_sub:
-      line["sub"] = sub_records(dev, peaks, args.sub_iters, 20)
+      line["sub"] = sub_records(dev, peaks, args.sub_iters, 8)
     if world == 1 and not args.no_cpu_baseline:
       tf, cores, sample = cpu_reference_sample(budget_s=15.0)
       line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample}

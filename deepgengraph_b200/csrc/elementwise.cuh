@@ -5,6 +5,8 @@
 // SM count.
 #pragma once
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -51,6 +53,31 @@ __device__ __forceinline__ uint4 pack16(const float (&f)[16 / sizeof(T)]) {
   return raw;
 }
 
+// y = T(x * inv) * w with the last product taken in T (csrc/norm.cu:54), for one 16-byte vector.  For the 16-bit
+// types the product of the two T values is one packed multiply (a single rounding, the same result as the fp32
+// product rounded once): a third of the instructions of the convert-multiply-convert form.
+template <typename T>
+__device__ __forceinline__ uint4 scale_round_mul(const float (&x)[16 / sizeof(T)], float inv, const uint4& w_raw) {
+  uint4 out;
+  if constexpr (sizeof(T) == 4) {
+    const float* w = reinterpret_cast<const float*>(&w_raw);
+    float* o = reinterpret_cast<float*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = (x[i] * inv) * w[i];
+  } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&w_raw);
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o2[i] = __hmul2(__floats2bfloat162_rn(x[2 * i] * inv, x[2 * i + 1] * inv), w2[i]);
+  } else {
+    const __half2* w2 = reinterpret_cast<const __half2*>(&w_raw);
+    __half2* o2 = reinterpret_cast<__half2*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o2[i] = __hmul2(__floats2half2_rn(x[2 * i] * inv, x[2 * i + 1] * inv), w2[i]);
+  }
+  return out;
+}
+
 __device__ __forceinline__ uint4 ld_nc_16(const void* p) {  // streaming read, no L1 allocation
   uint4 v;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
@@ -88,8 +115,8 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // phase re-reads the ROUNDED residual like csrc/norm.cu:80 (variance from the
 // unrounded sum, csrc/norm.cu:68-70).
 // ---------------------------------------------------------------------------
-template <typename T, int MAXV, bool FUSED_ADD>
-__global__ void __launch_bounds__(256)
+template <typename T, int MAXV, bool FUSED_ADD, int THREADS>
+__global__ void __launch_bounds__(THREADS)
 rms_norm_rows_kernel(T* __restrict__ out, T* __restrict__ input, T* __restrict__ residual,
                      const T* __restrict__ weight, float epsilon, int64_t num_tokens, int hidden) {
   // One WARP per row: the row lives in the warp's registers as raw 16-byte vectors (lane l holds vectors
@@ -98,17 +125,18 @@ rms_norm_rows_kernel(T* __restrict__ out, T* __restrict__ input, T* __restrict__
   constexpr int VN = 16 / sizeof(T);
   const int nvec = hidden / VN;  // hidden % VN == 0 checked on the host
   const int lane = threadIdx.x & 31;
-  const int64_t warp_global = (int64_t)blockIdx.x * (256 / 32) + (threadIdx.x >> 5);
-  const int64_t warp_count = (int64_t)gridDim.x * (256 / 32);
+  const int64_t warp_global = (int64_t)blockIdx.x * (THREADS / 32) + (threadIdx.x >> 5);
+  const int64_t warp_count = (int64_t)gridDim.x * (THREADS / 32);
   for (int64_t row = warp_global; row < num_tokens; row += warp_count) {
     T* in_row = input + row * hidden;
     uint4 raw[MAXV];
     float ss = 0.f;
     if constexpr (FUSED_ADD) {
       T* res_row = residual + row * hidden;
-      // all loads of the row are issued before the first store (a store in between would order the later loads
-      // behind it); for the widest rows the residual is consumed in two halves to stay within the register file
-      constexpr int HV = MAXV > 16 ? MAXV / 2 : MAXV;
+      // the input row is loaded whole, the residual row in two halves (each half's loads are issued together, before
+      // that half's stores): the second operand never needs more than half a row of registers, which lets more
+      // rows be resident per SM
+      constexpr int HV = MAXV >= 8 ? (MAXV + 1) / 2 : MAXV;
 #pragma unroll
       for (int v = 0; v < MAXV; ++v) {
         const int idx = lane + v * 32;
@@ -162,12 +190,9 @@ rms_norm_rows_kernel(T* __restrict__ out, T* __restrict__ input, T* __restrict__
     for (int v = 0; v < MAXV; ++v) {
       const int idx = lane + v * 32;
       if (idx < nvec) {
-        float x[VN], w[VN], y[VN];
+        float x[VN];
         unpack16<T>(raw[v], x);
-        unpack16<T>(ld_16(weight + (int64_t)idx * VN), w);
-#pragma unroll
-        for (int i = 0; i < VN; ++i) y[i] = to_f32<T>(from_f32<T>(x[i] * inv)) * w[i];
-        st_16(out_row + (int64_t)idx * VN, pack16<T>(y));
+        st_16(out_row + (int64_t)idx * VN, scale_round_mul<T>(x, inv, ld_16(weight + (int64_t)idx * VN)));
       }
     }
   }
@@ -215,13 +240,19 @@ int launch_rms_norm(void* out, void* input, void* residual, const void* weight, 
   T* res = (T*)residual;
   const T* w = (const T*)weight;
   if (vec_ok && nvec <= 32 * 32) {
-    // 8 rows (warps) per block; enough blocks to give every SM several resident warps per scheduler
-    const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((num_tokens + 7) / 8, (int64_t)sms * 8));
+    // One row per warp, small blocks (4 warps): the register footprint of a row (MAXV 16-byte vectors per lane) limits
+    // an SM to a few hundred resident threads, and with small blocks those threads belong to several blocks that
+    // start and finish at different times, so the load phase of one block overlaps the store phase of another.
+    constexpr int TH = 128;
+    static const int env_grid = std::getenv("B200_RMS_GRID_PER_SM") ? std::atoi(std::getenv("B200_RMS_GRID_PER_SM")) : 0;
+    const int per_sm = env_grid > 0 ? env_grid : 16;
+    const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((num_tokens + TH / 32 - 1) / (TH / 32), (int64_t)sms * per_sm));
 #define B200_RMS_LAUNCH(MAXV_) \
-  rms_norm_rows_kernel<T, MAXV_, FUSED_ADD><<<grid, 256, 0, stream>>>(o, in, res, w, eps, num_tokens, hidden)
+  rms_norm_rows_kernel<T, MAXV_, FUSED_ADD, TH><<<grid, TH, 0, stream>>>(o, in, res, w, eps, num_tokens, hidden)
     if (nvec <= 64) B200_RMS_LAUNCH(2);
     else if (nvec <= 128) B200_RMS_LAUNCH(4);
     else if (nvec <= 256) B200_RMS_LAUNCH(8);
+    else if (nvec <= 448) B200_RMS_LAUNCH(14);
     else if (nvec <= 512) B200_RMS_LAUNCH(16);
     else B200_RMS_LAUNCH(32);
 #undef B200_RMS_LAUNCH
@@ -354,22 +385,43 @@ rotary_online_kernel(const int32_t* __restrict__ positions, T* __restrict__ quer
     if (vec_ok) {
       constexpr int VPH = HALF / VN;  // vectors per half head
       const int total = (heads + kv_heads) * VPH;
-      for (int g = lane; g < total; g += 32) {
-        const int head = g / VPH;
-        const int c = (g - head * VPH) * VN;
-        T* base = (head < heads) ? query + tok * q_stride + (int64_t)head * HEAD_DIM
-                                 : key + tok * k_stride + (int64_t)(head - heads) * HEAD_DIM;
-        float x[VN], y[VN], ox[VN], oy[VN];
-        unpack16<T>(ld_16(base + c), x);
-        unpack16<T>(ld_16(base + HALF + c), y);
+      // U element pairs per lane and step: all 2 * U 16-byte loads are issued before the first store, so that a
+      // warp keeps 4 KB in flight (with one pair per step the kernel was bound by load latency at ~70 % of the
+      // copy rate)
+      constexpr int U = 4;
+      for (int g0 = lane; g0 < total; g0 += 32 * U) {
+        T* base[U];
+        int col[U];
+        uint4 rx[U], ry[U];
 #pragma unroll
-        for (int i = 0; i < VN; ++i) {
-          const float cs = s_cos[c + i], sn = s_sin[c + i];
-          ox[i] = x[i] * cs - y[i] * sn;
-          oy[i] = y[i] * cs + x[i] * sn;
+        for (int u = 0; u < U; ++u) {
+          const int g = g0 + 32 * u;
+          if (g < total) {
+            const int head = g / VPH;
+            col[u] = (g - head * VPH) * VN;
+            base[u] = (head < heads) ? query + tok * q_stride + (int64_t)head * HEAD_DIM
+                                     : key + tok * k_stride + (int64_t)(head - heads) * HEAD_DIM;
+            rx[u] = ld_16(base[u] + col[u]);
+            ry[u] = ld_16(base[u] + HALF + col[u]);
+          }
         }
-        st_16(base + c, pack16<T>(ox));
-        st_16(base + HALF + c, pack16<T>(oy));
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (g0 + 32 * u < total) {
+            const int c = col[u];
+            float x[VN], y[VN], ox[VN], oy[VN];
+            unpack16<T>(rx[u], x);
+            unpack16<T>(ry[u], y);
+#pragma unroll
+            for (int i = 0; i < VN; ++i) {
+              const float cs = s_cos[c + i], sn = s_sin[c + i];
+              ox[i] = x[i] * cs - y[i] * sn;
+              oy[i] = y[i] * cs + x[i] * sn;
+            }
+            st_16(base[u] + c, pack16<T>(ox));
+            st_16(base[u] + HALF + c, pack16<T>(oy));
+          }
+        }
       }
     } else {
       const int total = (heads + kv_heads) * HALF;
