@@ -344,7 +344,14 @@ def sub_records(dev, peaks, iters, warmup):
   record("config4_keyformer", "config4: B2 H32 S2048 D128 bf16 causal, tau 1.0, Gumbel noise tensor input (1.07 GB)",
          lambda: att.attn_kf_fwd(q, k, v, exp_rand, tau=1.0), "hbm", bytes4,
          {"tflops_credited": causal_flops(b4, h4, s4, D) / 1e12, "note": "noise counted once in the algorithmic bytes"})
-  del exp_rand, q, k, v
+  del exp_rand
+  # the same scores with the noise generated inside the kernels (Philox4x32-10 keyed by seed and position): nothing of
+  # size S x S is read; the sweeps are then bound by integer/issue throughput (about 35 instructions per element for
+  # the generator, the Gumbel mapping and the quad exchange), so the tensor figure is the credited attention FLOPs
+  record("config4_keyformer_generated_noise", "config4 shape, noise generated in the kernels from a seed (no 1.07 GB input)",
+         lambda: att.attn_kf_fwd(q, k, v, None, tau=1.0, seed=11), "tensor", causal_flops(b4, h4, s4, D),
+         {"note": "issue-bound: counter-based generator, two log2 and one exp2 per element and sweep"})
+  del q, k, v
 
   # ---- config 5: attention, whole Gemma-2-style layer, bandwidth ops ----
   cfg = L.Gemma2LayerConfig()

@@ -39,6 +39,9 @@ SIGNATURES = {
     "b200_attn_score": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]),
     "b200_attn_score_gqa": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f,
                                  _vp]),
+    "b200_attn_kf_score_seeded": (_i, [_vp, _vp, _vp, ctypes.c_uint64, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _f,
+                                       _f, _vp]),
+    "b200_kf_noise_fill": (_i, [_vp, ctypes.c_uint64, _i, _i, _i, _i, _vp]),
     "b200_attn_kf_score_gqa": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]),
     "b200_attn_score_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]),
     "b200_attn_corm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i, _f, _vp]),

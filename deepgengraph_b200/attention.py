@@ -2,7 +2,8 @@
 
   attn_fwd(q, k, v, causal=True, window=-1, softcap=0.0, scale=None) -> out
   attn_score_fwd(q, k, v, want_sq=False, ...)                       -> (out, colsum[, colsum_sq])
-  attn_kf_fwd(q, k, v, exp_rand, tau, ...)                          -> (out, kf_score)
+  attn_kf_fwd(q, k, v, exp_rand | None, tau, ..., seed)             -> (out, kf_score)
+  kf_noise(seed, batch, heads, q_len, kv_len, device)               -> exp_rand of the in-kernel generator
   attn_snapkv_fwd(q, k, v, kernel_size=5, ...)                      -> (out, pooled colsum)
   attn_corm_fwd(q, k, v, ...)                                       -> (out, bool flags)
 
@@ -159,6 +160,68 @@ def _attn_corm_impl(q, k, v, causal, scale):
   return out, flags.view(torch.bool)
 
 
+def philox4x32_10(c0, c1, c2, c3, k0, k1):
+  """Philox4x32-10 (Salmon et al., SC'11) on int64 tensors that hold 32-bit words; k0, k1 are Python ints.
+  Returns the four output words.  The same function as philox4x32_10 in csrc/attn_sweep.cuh."""
+  m32 = 0xFFFFFFFF
+  for _ in range(10):
+    p0, p1 = c0 * 0xD2511F53, c2 * 0xCD9E8D57       # 64-bit products; int64 wrap-around keeps the bit pattern
+    c0, c1, c2, c3 = ((p1 >> 32) & m32) ^ c1 ^ k0, p1 & m32, ((p0 >> 32) & m32) ^ c3 ^ k1, p0 & m32
+    k0, k1 = (k0 + 0x9E3779B9) & m32, (k1 + 0xBB67AE85) & m32
+  return c0, c1, c2, c3
+
+
+def kf_noise(seed, batch, heads, q_len, kv_len, device="cpu"):
+  """The exp_rand tensor float32 [batch, heads, q_len, kv_len] that attn_kf_fwd(..., exp_rand=None, seed=seed)
+  generates inside its kernels: element (b, h, i, j) is word j & 3 of Philox4x32-10 at counter (j >> 2, i, b * heads +
+  h, 0) under key (seed & 0xffffffff, seed >> 32), mapped to u = ((word >> 9) + 1/2) * 2^-23 and exp_rand = -ln(u)
+  (so -ln(exp_rand) is Gumbel(0, 1) noise).  Plain torch integer arithmetic: runs on any device, so a CPU reference
+  of the reference's KeyFormer module (kernels/kf.py:19-42) can be fed exactly the noise the kernels use."""
+  dev = torch.device(device)
+  nq = (kv_len + 3) // 4
+  jq = torch.arange(nq, dtype=torch.int64, device=dev).view(1, 1, nq)
+  i = torch.arange(q_len, dtype=torch.int64, device=dev).view(1, q_len, 1)
+  bh = torch.arange(batch * heads, dtype=torch.int64, device=dev).view(batch * heads, 1, 1)
+  shape = (batch * heads, q_len, nq)
+  words = philox4x32_10(jq.expand(shape), i.expand(shape), bh.expand(shape), torch.zeros(shape, dtype=torch.int64, device=dev),
+                        int(seed) & 0xFFFFFFFF, (int(seed) >> 32) & 0xFFFFFFFF)
+  r = torch.stack(words, dim=-1).reshape(batch * heads, q_len, nq * 4)[:, :, :kv_len]
+  u = ((r >> 9).double() + 0.5) * (1.0 / 8388608.0)
+  return (-torch.log(u)).float().view(batch, heads, q_len, kv_len)
+
+
+def kf_noise_fill(seed, batch, heads, q_len, kv_len, device):
+  """kf_noise evaluated by the library's own fill kernel (b200_kf_noise_fill): same tensor, on the GPU."""
+  dev = torch.device(device)
+  out = torch.empty((batch, heads, q_len, kv_len), dtype=torch.float32, device=dev)
+  with torch.cuda.device(dev):
+    st = _lib.load().b200_kf_noise_fill(out.data_ptr(), int(seed) & 0xFFFFFFFFFFFFFFFF, batch, heads, q_len, kv_len,
+                                        _stream_ptr(dev))
+  _lib.check(st, "kf_noise_fill")
+  return out
+
+
+def _attn_kf_seeded_impl(q, k, v, seed, tau, causal, scale):
+  where = "attn_kf_fwd"
+  dev = _check_qkv(where, q, k, v)
+  B, Sq, H, D = q.shape
+  Skv, Hk = k.size(1), k.size(2)
+  if scale is None or scale <= 0:
+    scale = 1.0 / math.sqrt(D)
+  out = torch.empty_like(q)
+  score = torch.empty((B, Hk, Skv), dtype=torch.float32, device=dev)
+  if B == 0 or Sq == 0:
+    return out, score.zero_()
+  ws, nbytes = _workspace(dev, B, Sq, Skv, H)
+  with torch.cuda.device(dev):
+    st = _lib.load().b200_attn_kf_score_seeded(q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                               int(seed) & 0xFFFFFFFFFFFFFFFF, out.data_ptr(), score.data_ptr(),
+                                               ws.data_ptr(), nbytes, B, Sq, Skv, H, Hk, D, _dtype_code(q, where),
+                                               int(bool(causal)), float(tau), float(scale), _stream_ptr(dev))
+  _lib.check(st, where)
+  return out, score
+
+
 def _attn_kf_impl(q, k, v, exp_rand, tau, causal, scale):
   where = "attn_kf_fwd"
   dev = _check_qkv(where, q, k, v)
@@ -237,6 +300,17 @@ def _(q, k, v, exp_rand, tau, causal, scale):
   return torch.empty_like(q), q.new_empty((q.size(0), k.size(2), k.size(1)), dtype=torch.float32)
 
 
+@torch.library.custom_op("b200attn::attn_kf_seeded_fwd", mutates_args=())
+def _op_attn_kf_seeded_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seed: int, tau: float, causal: bool,
+                           scale: float) -> tuple[torch.Tensor, torch.Tensor]:
+  return _attn_kf_seeded_impl(q, k, v, seed, tau, causal, scale)
+
+
+@_op_attn_kf_seeded_fwd.register_fake
+def _(q, k, v, seed, tau, causal, scale):
+  return torch.empty_like(q), q.new_empty((q.size(0), k.size(2), k.size(1)), dtype=torch.float32)
+
+
 @torch.library.custom_op("b200attn::attn_snapkv_fwd", mutates_args=())
 def _op_attn_snapkv_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel_size: int, causal: bool,
                         scale: float) -> tuple[torch.Tensor, torch.Tensor]:
@@ -283,9 +357,13 @@ def attn_score_fwd(q, k, v, want_sq=False, causal=True, window=-1, softcap=0.0, 
 
 
 @traced
-def attn_kf_fwd(q, k, v, exp_rand, tau=1.5, causal=True, scale=None):
+def attn_kf_fwd(q, k, v, exp_rand=None, tau=1.5, causal=True, scale=None, seed=0):
   """Attention output + KeyFormer score: column sums of softmax((logits - log(exp_rand)) / tau)
-  (kernels/kf.py:36-42)."""
+  (kernels/kf.py:36-42).  exp_rand float32 [B, H, Sq, Skv] as the reference passes it -- or None: the kernels then
+  generate the noise themselves from `seed` (the tensor kf_noise(seed, ...) describes), and nothing of size
+  Sq x Skv is read or stored."""
+  if exp_rand is None:
+    return _op_attn_kf_seeded_fwd(q, k, v, int(seed), float(tau), bool(causal), float(scale or 0.0))
   return _op_attn_kf_fwd(q, k, v, exp_rand, float(tau), bool(causal), float(scale or 0.0))
 
 

@@ -40,6 +40,53 @@ enum SweepAux : int { AUX_NONE = 0, AUX_SQUARES = 1, AUX_CORM = 2 };
 #endif
 constexpr int kSweepPolyOf8 = B200_SWEEP_POLY_OF_8;
 
+// ---------------------------------------------------------------------------------------------
+// In-kernel noise for the KeyFormer sweeps (no counterpart in the reference, whose modules take the noise as a
+// [B, H, Sq, Skv] fp32 tensor, kernels/kf.py:19,36-37, drawn by the caller, kf.py:48 / models/kf.py:44).
+// Philox4x32-10 (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3", SC'11), a counter-based
+// generator: the four 32-bit outputs of counter (j >> 2, i, b * heads + h, 0) under key (seed_lo, seed_hi) belong to
+// query i and keys 4 * (j >> 2) .. + 3, so any (query, key) element can be produced anywhere, in any order.
+// Output word r maps to u = ((r >> 9) + 1/2) * 2^-23 in (0, 1) and exp_rand = -ln(u), which makes -ln(exp_rand) an
+// exact Gumbel(0, 1) variate; deepgengraph_b200.attention.kf_noise materialises the same tensor on the host side.
+// ---------------------------------------------------------------------------------------------
+__host__ __device__ __forceinline__ void philox4x32_10(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c[0], p1 = (uint64_t)0xCD9E8D57u * c[2];
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c[1] ^ k0, n2 = (uint32_t)(p0 >> 32) ^ c[3] ^ k1;
+    c[1] = (uint32_t)p1;
+    c[3] = (uint32_t)p0;
+    c[0] = n0;
+    c[2] = n2;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+}
+
+// log2(exp_rand) of one Philox output word.  exp_rand = -ln(u): for u within 2^-8 of one the logarithm comes from the
+// series -ln(1 - v) = v + v^2/2 + v^3/3 (lg2.approx has an ABSOLUTE error of 2^-22 on (0.5, 2), which near u = 1 is
+// as large as the result itself); elsewhere from lg2.approx.  Relative error of exp_rand below 5e-5 everywhere.
+__device__ __forceinline__ float kf_gen_log2_exp_rand(uint32_t r) {
+  const float t = __uint_as_float(0x3f800000u | (r >> 9)) - 1.0f;      // k * 2^-23, exact
+  const float u = t + 5.9604644775390625e-08f;                         // + 2^-24: exact, in (0, 1)
+  const float v = 0.99999994039535522461f - t;                         // 1 - u, exact
+  const float series = v * fmaf(v, fmaf(v, 0.33333334f, 0.5f), 1.0f);
+  const float e = v < 0.00390625f ? series : -lg2_approx(u) * 0.69314718055994530942f;
+  return lg2_approx(e);
+}
+
+// x[u] <- x[u ^ c] for c in 0..3 (two conditional swap stages)
+__device__ __forceinline__ void xor_permute4(uint32_t (&x)[4], uint32_t c) {
+  if (c & 1u) {
+    uint32_t t = x[0]; x[0] = x[1]; x[1] = t;
+    t = x[2]; x[2] = x[3]; x[3] = t;
+  }
+  if (c & 2u) {
+    uint32_t t = x[0]; x[0] = x[2]; x[2] = t;
+    t = x[1]; x[1] = x[3]; x[3] = t;
+  }
+}
+
 struct SweepParams {
   const float* lse;     // [B*H][lse_stride]  row normalisers (COLSUM: L, KF_COLSUM: Lz)
   float* lse_out;       // [B*H][lse_stride]  KF_ROWLSE output
@@ -52,6 +99,7 @@ struct SweepParams {
   const uint16_t* a_base;   // K (column-sum sweeps) or Q (row-LSE sweep), [batch, rows, a_heads, 128]
   int a_rows, a_heads;
   float scale_log2, cap_in, cap_out, inv_tau;
+  uint32_t seed_lo, seed_hi;   // key of the in-kernel noise generator (KeyFormer sweeps without a noise tensor)
 };
 
 // CWG_ = compute warpgroups per CTA.  With two, warpgroup g reduces columns [g * BX/2, (g+1) * BX/2) of every
@@ -59,11 +107,14 @@ struct SweepParams {
 // added once at the end: twice the warps per scheduler hide the TMEM-load, shared-memory and special-function
 // latencies of the element loop, which with one warp per scheduler and CTA bound the sweep (measured: special-
 // function unit 55 % busy, issue slots 37 %, moving exponentials to the FMA pipe changed nothing).
-template <int MODE_, int BX_, int STAGES_, int CWG_ = 1>
+// GEN_ (KeyFormer sweeps): the noise comes from the in-kernel generator instead of a tensor -- no noise stages.
+template <int MODE_, int BX_, int STAGES_, int CWG_ = 1, bool GEN_ = false>
 struct SweepCfg {
   static constexpr int MODE = MODE_, BX = BX_, STAGES = STAGES_, CWG = CWG_;
   static constexpr int D = 128, BM = 128;
-  static constexpr bool NOISE = MODE != SWEEP_COLSUM;
+  static constexpr bool GEN = GEN_;
+  static_assert(!GEN || MODE != SWEEP_COLSUM, "only the KeyFormer sweeps use noise");
+  static constexpr bool NOISE = MODE != SWEEP_COLSUM && !GEN;   // noise TENSOR streamed through the auxiliary ring
   static constexpr bool LSE_IN = MODE != SWEEP_KF_ROWLSE;
   // BX = 64: the stationary tile lives in TMEM (64 columns beside the two 64-column product tiles) and is the
   // A operand of the MMAs, which then read only the streamed operand from shared memory -- with both operands
@@ -80,7 +131,8 @@ struct SweepCfg {
   static constexpr int TMEM_COLS = A_TMEM ? 256 : 2 * BX;               // two product tiles (+ the stationary tile)
   static constexpr int COMPUTE_WARPS = 4 * CWG;
   static constexpr int THREADS = (COMPUTE_WARPS + 2) * 32;   // + TMA producer warp + MMA issuer warp
-  static constexpr int CTAS_PER_SM = CWG == 2 ? 2 : 1;       // launch bound (registers): two 320-thread CTAs share an SM
+  // launch bound (registers): two CTAs share an SM -- the 320-thread column-sum CTAs and the KeyFormer CTAs
+  static constexpr int CTAS_PER_SM = (CWG == 2 || MODE != SWEEP_COLSUM) ? 2 : 1;
   static_assert(CWG == 1 || (CWG == 2 && BX == 128 && !A_TMEM), "two compute warpgroups: 128-wide blocks only");
   static constexpr int BAR_A_FULL = 0;
   static constexpr int BAR_X_FULL = 1;
@@ -268,7 +320,7 @@ __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, con
   float2 acc2 = make_float2(0.f, 0.f), sq2 = make_float2(0.f, 0.f);
   // One 32-column chunk of the tile: p = exp2(x - L_i) for the thread's key against 32 queries.
   auto chunk_body = [&](auto mask_tag, const uint32_t (&sr)[32], int ch, const float* lse_s, const float* noise_col,
-                        int lo_c, int hi_c, float qbase) {
+                        int lo_c, int hi_c, float qbase, int i0) {
     constexpr bool MASK = decltype(mask_tag)::value;
     const float2 c2 = make_float2(cmul, cmul);
 #pragma unroll
@@ -284,8 +336,24 @@ __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, con
       if constexpr (KF) {
         const float2 it2 = make_float2(p.inv_tau, p.inv_tau);
         float g[4];
+        if constexpr (Cfg::GEN) {
+          // One generator call yields the noise of ONE query against four consecutive keys, while this thread needs
+          // one key against four consecutive queries: the four lanes of a quad (keys 4k .. 4k+3) each generate one of
+          // the four queries and exchange the words (lane c sends word c ^ s to lane c ^ s in round s).
+          const uint32_t cpos = lane & 3;
+          uint32_t o[4] = {(uint32_t)key >> 2, (uint32_t)(i0 + ch * 32 + i) + cpos, (uint32_t)c.bh, 0u};
+          philox4x32_10(o, p.seed_lo, p.seed_hi);
+          xor_permute4(o, cpos);
+          uint32_t r[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) g[u] = -lg2_approx(noise_col[(ch * 32 + i + u) * 32]);
+          for (int sft = 0; sft < 4; ++sft) r[sft] = __shfl_sync(0xffffffffu, o[sft], (lane & ~3) | (int)(cpos ^ sft));
+          xor_permute4(r, cpos);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) g[u] = -kf_gen_log2_exp_rand(r[u]);
+        } else {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) g[u] = -lg2_approx(noise_col[(ch * 32 + i + u) * 32]);
+        }
         e0 = ffma2(ffma2(make_float2(sv[0], sv[1]), c2, make_float2(g[0], g[1])), it2, make_float2(-L.x, -L.y));
         e1 = ffma2(ffma2(make_float2(sv[2], sv[3]), c2, make_float2(g[2], g[3])), it2, make_float2(-L.z, -L.w));
       } else {
@@ -355,9 +423,9 @@ __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, con
       tmem_ld_wait();
       if (cc + 1 < NCH) tmem_ld32(lane_addr + tb * BX + (ch + 1) * 32, sr[(cc + 1) & 1]);
       if (need_mask)
-        chunk_body(std::true_type{}, sr[cc & 1], ch, lse_s, noise_col, lo_c, hi_c, (float)(i0 + 1));
+        chunk_body(std::true_type{}, sr[cc & 1], ch, lse_s, noise_col, lo_c, hi_c, (float)(i0 + 1), i0);
       else
-        chunk_body(std::false_type{}, sr[cc & 1], ch, lse_s, noise_col, lo_c, hi_c, (float)(i0 + 1));
+        chunk_body(std::false_type{}, sr[cc & 1], ch, lse_s, noise_col, lo_c, hi_c, (float)(i0 + 1), i0);
       if (tl_on && cc < 4) B200_TL(tl_base + 3 + cc);
     }
     // this TMEM buffer and this auxiliary stage may be refilled
@@ -495,9 +563,10 @@ __device__ __forceinline__ void sweep_compute_rowlse(const SweepCtx<Cfg>& c, con
   for (int blk = c.blk_lo; blk < c.blk_hi; ++blk) {
     const int n = blk - c.blk_lo, st = n % ST, tb = n & 1;
     if (!mbar_wait(&c.bars[Cfg::BAR_T_FULL + tb], (n >> 1) & 1, c.abort_flag, WAIT_T_FULL)) return;
-    if (!mbar_wait(&c.bars[Cfg::BAR_N_FULL + st], (n / ST) & 1, c.abort_flag, WAIT_N_FULL)) return;
+    if constexpr (Cfg::N_STAGE_BYTES > 0)
+      if (!mbar_wait(&c.bars[Cfg::BAR_N_FULL + st], (n / ST) & 1, c.abort_flag, WAIT_N_FULL)) return;
     tc_fence_after();
-    const uint8_t* nst = c.sN + st * Cfg::N_STAGE_STRIDE;
+    [[maybe_unused]] const uint8_t* nst = c.sN + st * Cfg::N_STAGE_STRIDE;
     const int hi_c = hi_key - blk * BX;
     float z[BX];
     float mx = -INFINITY;
@@ -506,16 +575,24 @@ __device__ __forceinline__ void sweep_compute_rowlse(const SweepCtx<Cfg>& c, con
       uint32_t sr[32];
       tmem_ld32(lane_addr + tb * BX + ch * 32, sr);
       tmem_ld_wait();
-      const uint8_t* panel = nst + ch * (128 * 128) + r_local * 128;
+      [[maybe_unused]] const uint8_t* panel = nst + ch * (128 * 128) + r_local * 128;
 #pragma unroll
       for (int q4 = 0; q4 < 8; ++q4) {
-        // 128-byte swizzle written by TMA: 16-byte chunk q4 of row r sits at chunk (q4 ^ (r & 7))
-        const float4 er = *reinterpret_cast<const float4*>(panel + ((q4 ^ (r_local & 7)) << 4));
-        const float ev[4] = {er.x, er.y, er.z, er.w};
+        float lg[4];   // log2(exp_rand) of this query against four consecutive keys
+        if constexpr (Cfg::GEN) {
+          uint32_t o[4] = {(uint32_t)(blk * BX + ch * 32 + q4 * 4) >> 2, (uint32_t)row, (uint32_t)c.bh, 0u};
+          philox4x32_10(o, p.seed_lo, p.seed_hi);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) lg[u] = kf_gen_log2_exp_rand(o[u]);
+        } else {
+          // 128-byte swizzle written by TMA: 16-byte chunk q4 of row r sits at chunk (q4 ^ (r & 7))
+          const float4 er = *reinterpret_cast<const float4*>(panel + ((q4 ^ (r_local & 7)) << 4));
+          lg[0] = lg2_approx(er.x), lg[1] = lg2_approx(er.y), lg[2] = lg2_approx(er.z), lg[3] = lg2_approx(er.w);
+        }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           const int col = ch * 32 + q4 * 4 + u;
-          float v = fmaf(__uint_as_float(sr[q4 * 4 + u]), cz, -lg2_approx(ev[u]) * p.inv_tau);
+          float v = fmaf(__uint_as_float(sr[q4 * 4 + u]), cz, -lg[u] * p.inv_tau);
           if (col > hi_c) v = -INFINITY;
           z[col] = v;
           mx = fmaxf(mx, v);
@@ -526,7 +603,7 @@ __device__ __forceinline__ void sweep_compute_rowlse(const SweepCtx<Cfg>& c, con
     __syncwarp();
     if (lane == 0) {
       mbar_arrive(&c.bars[Cfg::BAR_T_EMPTY + tb]);
-      mbar_arrive(&c.bars[Cfg::BAR_N_EMPTY + st]);
+      if constexpr (Cfg::N_STAGE_BYTES > 0) mbar_arrive(&c.bars[Cfg::BAR_N_EMPTY + st]);
     }
     const float m_new = fmaxf(m, mx);
     float s0 = 0.f, s1 = 0.f;
@@ -546,11 +623,13 @@ __device__ __forceinline__ void sweep_compute_rowlse(const SweepCtx<Cfg>& c, con
 // tile that meets the most streamed blocks first, z = chunk of streamed blocks.  Blocks are dispatched x-fastest,
 // so the launch walks ALL units' heaviest tiles first and ends on the lightest ones (longest-processing-time-first
 // over the whole launch, not per head): under a causal mask a tile's work ranges from one block to all of them.
-template <int MODE, int BX, int STAGES, bool BF16, bool SOFTCAP, int AUX, bool GROUPED = false, int CWG = 1>
-__global__ void __launch_bounds__((SweepCfg<MODE, BX, STAGES, CWG>::THREADS), (SweepCfg<MODE, BX, STAGES, CWG>::CTAS_PER_SM))
+template <int MODE, int BX, int STAGES, bool BF16, bool SOFTCAP, int AUX, bool GROUPED = false, int CWG = 1,
+          bool GEN = false>
+__global__ void __launch_bounds__((SweepCfg<MODE, BX, STAGES, CWG, GEN>::THREADS),
+                                  (SweepCfg<MODE, BX, STAGES, CWG, GEN>::CTAS_PER_SM))
 attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_x,
                   const __grid_constant__ CUtensorMap tm_n, const SweepParams p) {
-  using Cfg = SweepCfg<MODE, BX, STAGES, CWG>;
+  using Cfg = SweepCfg<MODE, BX, STAGES, CWG, GEN>;
   constexpr int CW = Cfg::COMPUTE_WARPS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -697,6 +776,27 @@ score_reduce_kernel(float* __restrict__ out, float* __restrict__ out_sq, const f
   }
 }
 
+// exp_rand[b, h, i, j] of the in-kernel generator, written out as the tensor the reference's KeyFormer module takes
+// (kernels/kf.py:19): one thread per four consecutive keys.  The logarithm is taken in double precision, so the
+// tensor is the correctly rounded -ln(u); the sweeps' own evaluation differs from it by < 5e-5 relative.
+__global__ void __launch_bounds__(256)
+kf_noise_fill_kernel(float* __restrict__ out, int64_t rows, int q_len, int kv_len, uint32_t seed_lo, uint32_t seed_hi) {
+  const int64_t quads_per_row = (kv_len + 3) / 4;
+  const int64_t total = rows * quads_per_row;
+  for (int64_t g = (int64_t)blockIdx.x * 256 + threadIdx.x; g < total; g += (int64_t)gridDim.x * 256) {
+    const int64_t row = g / quads_per_row;            // (b * heads + h) * q_len + i
+    const uint32_t jq = (uint32_t)(g - row * quads_per_row);
+    const int64_t bh = row / q_len;
+    uint32_t o[4] = {jq, (uint32_t)(row - bh * q_len), (uint32_t)bh, 0u};
+    philox4x32_10(o, seed_lo, seed_hi);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t j = (int64_t)jq * 4 + u;
+      if (j < kv_len) out[row * kv_len + j] = (float)(-log(((double)(o[u] >> 9) + 0.5) * (1.0 / 8388608.0)));
+    }
+  }
+}
+
 // --------------------------------- host side ---------------------------------
 // size of the library's built-in scratch for b200_attn_score_static (32 MiB per GPU that loads the library)
 constexpr int64_t kStaticScoreScratchBytes = 32ll << 20;
@@ -751,11 +851,12 @@ inline int64_t score_workspace_bytes(int batch, int q_len, int kv_len, int heads
 }
 
 // n_chunks chunks of streamed blocks x n_tiles stationary tiles x (batch x heads) units -- (batch x K/V heads) when GROUPED
-template <int MODE, int BX, int STAGES, bool BF16, bool SOFTCAP, int AUX, bool GROUPED = false, int CWG = 1>
+template <int MODE, int BX, int STAGES, bool BF16, bool SOFTCAP, int AUX, bool GROUPED = false, int CWG = 1,
+          bool GEN = false>
 int launch_sweep(const CUtensorMap& ta, const CUtensorMap& tx, const CUtensorMap& tn, const SweepParams& p,
                  int n_chunks, int n_tiles, cudaStream_t stream) {
-  using Cfg = SweepCfg<MODE, BX, STAGES, CWG>;
-  auto kern = attn_sweep_kernel<MODE, BX, STAGES, BF16, SOFTCAP, AUX, GROUPED, CWG>;
+  using Cfg = SweepCfg<MODE, BX, STAGES, CWG, GEN>;
+  auto kern = attn_sweep_kernel<MODE, BX, STAGES, BF16, SOFTCAP, AUX, GROUPED, CWG, GEN>;
   static thread_local int configured_dev = -1;
   int dev = 0;
   B200_CUDA_TRY(cudaGetDevice(&dev));
@@ -927,14 +1028,16 @@ inline int attn_score_impl(const void* q, const void* k, const void* v, void* ou
 inline int attn_kf_impl(const void* q, const void* k, const void* v, const float* exp_rand, void* out,
                         float* kf_score, void* workspace, int64_t workspace_bytes, int batch, int q_len, int kv_len,
                         int heads, int head_dim, int dtype, int causal, float tau, float scale, cudaStream_t stream,
-                        int kv_heads = 0) {
+                        int kv_heads = 0, uint64_t seed = 0) {
+  // exp_rand == nullptr: the noise is generated in the kernels from `seed` (see philox4x32_10 above)
+  const bool gen = exp_rand == nullptr;
   if (kv_heads <= 0) kv_heads = heads;
   if (heads % kv_heads != 0) return B200_ERR_BAD_ARGUMENT;
   const int group = heads / kv_heads;
   int rc = score_common_checks(q, k, v, out, workspace, workspace_bytes, batch, q_len, kv_len, heads, head_dim, dtype);
   if (rc != B200_OK) return rc;
-  if (!exp_rand || !kf_score || !(tau > 0.f)) return B200_ERR_BAD_ARGUMENT;
-  if (kv_len % 4 != 0 || !aligned16(exp_rand)) return B200_ERR_MISALIGNED;
+  if (!kf_score || !(tau > 0.f)) return B200_ERR_BAD_ARGUMENT;
+  if (!gen && (kv_len % 4 != 0 || !aligned16(exp_rand))) return B200_ERR_MISALIGNED;
   if ((int64_t)batch * heads * q_len >= (1ll << 31)) return B200_ERR_UNSUPPORTED;
   const ScoreWorkspace w = score_workspace_layout(batch, q_len, kv_len, heads);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
@@ -952,8 +1055,13 @@ inline int attn_kf_impl(const void* q, const void* k, const void* v, const float
   if ((rc = make_bshd_tensor_map(&tk128, k, batch, kv_len, kv_heads, head_dim, 128, bf16)) != B200_OK) return rc;
   if ((rc = make_bshd_tensor_map(&tk64, k, batch, kv_len, kv_heads, head_dim, 64, bf16)) != B200_OK) return rc;
   const int64_t rows = (int64_t)batch * heads * q_len;
-  if ((rc = make_f32_matrix_tensor_map(&tn_rows128, exp_rand, rows, kv_len, 128, 32, true)) != B200_OK) return rc;
-  if ((rc = make_f32_matrix_tensor_map(&tn_rows64, exp_rand, rows, kv_len, 64, 32, false)) != B200_OK) return rc;
+  if (gen) {
+    tn_rows128 = tq128;   // unused
+    tn_rows64 = tq128;
+  } else {
+    if ((rc = make_f32_matrix_tensor_map(&tn_rows128, exp_rand, rows, kv_len, 128, 32, true)) != B200_OK) return rc;
+    if ((rc = make_f32_matrix_tensor_map(&tn_rows64, exp_rand, rows, kv_len, 64, 32, false)) != B200_OK) return rc;
+  }
 
   SweepParams p;
   std::memset(&p, 0, sizeof(p));
@@ -975,6 +1083,8 @@ inline int attn_kf_impl(const void* q, const void* k, const void* v, const float
   p.scale_log2 = scale * 1.4426950408889634f;
   p.inv_tau = 1.0f / tau;
   p.kv_group = group;
+  p.seed_lo = (uint32_t)seed;
+  p.seed_hi = (uint32_t)(seed >> 32);
 
   // sweep 1: Lz_i = log2 sum_j exp2(z_ij), one CTA per 128 queries
   const int q_tiles = (q_len + 127) / 128;
@@ -982,16 +1092,27 @@ inline int attn_kf_impl(const void* q, const void* k, const void* v, const float
   p.a_base = static_cast<const uint16_t*>(q);
   p.a_rows = q_len;
   p.a_heads = heads;
-  rc = bf16 ? launch_sweep<SWEEP_KF_ROWLSE, 64, B200_KF_STAGES, true, false, false>(tq128, tk64, tn_rows128, p, 1, q_tiles, stream)
-            : launch_sweep<SWEEP_KF_ROWLSE, 64, B200_KF_STAGES, false, false, false>(tq128, tk64, tn_rows128, p, 1, q_tiles, stream);
+#define B200_KF_SWEEP(MODE_, BF, GEN_, TA, TX, TN, NC, NT) \
+  launch_sweep<MODE_, 64, B200_KF_STAGES, BF, false, AUX_NONE, false, 1, GEN_>(TA, TX, TN, p, NC, NT, stream)
+  if (gen)
+    rc = bf16 ? B200_KF_SWEEP(SWEEP_KF_ROWLSE, true, true, tq128, tk64, tn_rows128, 1, q_tiles)
+              : B200_KF_SWEEP(SWEEP_KF_ROWLSE, false, true, tq128, tk64, tn_rows128, 1, q_tiles);
+  else
+    rc = bf16 ? B200_KF_SWEEP(SWEEP_KF_ROWLSE, true, false, tq128, tk64, tn_rows128, 1, q_tiles)
+              : B200_KF_SWEEP(SWEEP_KF_ROWLSE, false, false, tq128, tk64, tn_rows128, 1, q_tiles);
   if (rc != B200_OK) return rc;
   // sweep 2: per-key sums of exp2(z_ij - Lz_i)
   const int gy = w.kv_pad / 128;
   p.a_base = static_cast<const uint16_t*>(k);
   p.a_rows = kv_len;
   p.a_heads = kv_heads;
-  rc = bf16 ? launch_sweep<SWEEP_KF_COLSUM, 64, B200_KF_STAGES, true, false, false>(tk128, tq64, tn_rows64, p, p.n_chunks, gy, stream)
-            : launch_sweep<SWEEP_KF_COLSUM, 64, B200_KF_STAGES, false, false, false>(tk128, tq64, tn_rows64, p, p.n_chunks, gy, stream);
+  if (gen)
+    rc = bf16 ? B200_KF_SWEEP(SWEEP_KF_COLSUM, true, true, tk128, tq64, tn_rows64, p.n_chunks, gy)
+              : B200_KF_SWEEP(SWEEP_KF_COLSUM, false, true, tk128, tq64, tn_rows64, p.n_chunks, gy);
+  else
+    rc = bf16 ? B200_KF_SWEEP(SWEEP_KF_COLSUM, true, false, tk128, tq64, tn_rows64, p.n_chunks, gy)
+              : B200_KF_SWEEP(SWEEP_KF_COLSUM, false, false, tk128, tq64, tn_rows64, p.n_chunks, gy);
+#undef B200_KF_SWEEP
   if (rc != B200_OK) return rc;
 
   dim3 rgrid((kv_len + 255) / 256, batch * kv_heads);

@@ -332,6 +332,27 @@ int b200_attn_kf_score(const void* q, const void* k, const void* v, const float*
                       head_dim, dtype, causal, tau, scale, (cudaStream_t)stream);
 }
 
+int b200_attn_kf_score_seeded(const void* q, const void* k, const void* v, uint64_t seed, void* out, float* kf_score,
+                              void* workspace, int64_t workspace_bytes, int batch, int q_len, int kv_len, int heads,
+                              int kv_heads, int head_dim, int dtype, int causal, float tau, float scale, void* stream) {
+  if (kv_heads <= 0) return B200_ERR_BAD_ARGUMENT;
+  return attn_kf_impl(q, k, v, nullptr, out, kf_score, workspace, workspace_bytes, batch, q_len, kv_len, heads,
+                      head_dim, dtype, causal, tau, scale, (cudaStream_t)stream, kv_heads, seed);
+}
+
+int b200_kf_noise_fill(float* exp_rand, uint64_t seed, int batch, int heads, int q_len, int kv_len, void* stream) {
+  if (!exp_rand || batch < 0 || heads <= 0 || q_len < 0 || kv_len < 0) return B200_ERR_BAD_ARGUMENT;
+  const int64_t rows = (int64_t)batch * heads * q_len;
+  if (rows == 0 || kv_len == 0) return B200_OK;
+  if ((int64_t)batch * heads > 0xffffffffll) return B200_ERR_UNSUPPORTED;
+  const int64_t quads = rows * ((kv_len + 3) / 4);
+  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((quads + 255) / 256, (int64_t)sm_count() * 16));
+  kf_noise_fill_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(exp_rand, rows, q_len, kv_len, (uint32_t)seed,
+                                                               (uint32_t)(seed >> 32));
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
 int b200_attn_score_static(const void* q, const void* k, const void* v, void* out, float* score, float* score_sq,
                            int batch, int q_len, int kv_len, int heads, int head_dim, int dtype, int causal,
                            int window, float softcap, float scale, void* stream) {

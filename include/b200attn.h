@@ -269,6 +269,23 @@ int b200_attn_kf_score_gqa(const void* q, const void* k, const void* v, const fl
                            int kv_len, int heads, int kv_heads, int head_dim, int dtype, int causal, float tau,
                            float scale, void* stream);
 
+/*
+ * KeyFormer with the noise generated inside the kernels instead of read from a [batch, heads, q_len, kv_len] tensor
+ * (1.07 GB at batch 2 x 32 heads x seq 2048, 17 GB at seq 8192).  No counterpart in the reference, whose module takes
+ * the tensor (kernels/kf.py:19,36-37) from the caller (kf.py:48, models/kf.py:44).
+ * Element (b, h, i, j) comes from Philox4x32-10: counter (j >> 2, i, b * heads + h, 0), key (seed & 0xffffffff,
+ * seed >> 32), output word j & 3; word r maps to u = ((r >> 9) + 1/2) * 2^-23 and exp_rand = -ln(u), so that
+ * -ln(exp_rand) is a Gumbel(0, 1) variate.  b200_kf_noise_fill writes exactly that tensor (correctly rounded), so
+ * b200_attn_kf_score[_gqa] on the filled tensor and this entry point agree to the accuracy of the kernels' log2.
+ * kv_heads == heads or a divisor of it (scores are then the group mean, as in b200_attn_kf_score_gqa).
+ */
+int b200_attn_kf_score_seeded(const void* q, const void* k, const void* v, uint64_t seed, void* out, float* kf_score,
+                              void* workspace, int64_t workspace_bytes, int batch, int q_len, int kv_len, int heads,
+                              int kv_heads, int head_dim, int dtype, int causal, float tau, float scale, void* stream);
+
+/* exp_rand float32 [batch, heads, q_len, kv_len] of the generator above (see b200_attn_kf_score_seeded). */
+int b200_kf_noise_fill(float* exp_rand, uint64_t seed, int batch, int heads, int q_len, int kv_len, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
