@@ -22,7 +22,7 @@ import torch
 from .tracing import traced
 
 from . import _lib
-from .native_ops import _dtype_code, _require_cuda, _stream_ptr
+from .native_ops import _dtype_code, _on_device, _require_cuda, _stream_ptr
 
 
 def _row_strided(t):
@@ -62,7 +62,7 @@ def _attn_fwd_impl(q, k, v, causal, window, softcap, scale, want_lse=False):
   lse = torch.empty((B, H, Sq), dtype=torch.float32, device=dev) if want_lse else None
   if B == 0 or Sq == 0:   # empty batch / no queries: nothing to launch (the torch reference returns empty tensors)
     return (out, lse) if want_lse else out
-  with torch.cuda.device(dev):
+  with _on_device(dev):
     if q.is_contiguous() and k.is_contiguous() and v.is_contiguous():
       st = _lib.load().b200_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                                      lse.data_ptr() if want_lse else None, B, Sq, Skv, H, Hk, D,
@@ -104,7 +104,7 @@ def _attn_score_impl(q, k, v, want_sq, causal, window, softcap, scale):
   ws, nbytes = _workspace(dev, B, Sq, Skv, H)
   if H != Hk:
     # grouped-query attention: mean over the query heads of a K/V head, then the sums (kernels/roco.py:39-46)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
       st = _lib.load().b200_attn_score_gqa(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                                            score.data_ptr(), score_sq.data_ptr() if want_sq else None, None,
                                            ws.data_ptr(), nbytes, B, Sq, Skv, H, Hk, D, _dtype_code(q, where),
@@ -112,7 +112,7 @@ def _attn_score_impl(q, k, v, want_sq, causal, window, softcap, scale):
                                            _stream_ptr(dev))
     _lib.check(st, where)
     return (out, score, score_sq) if want_sq else (out, score)
-  with torch.cuda.device(dev):
+  with _on_device(dev):
     st = _lib.load().b200_attn_score(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), score.data_ptr(),
                                      score_sq.data_ptr() if want_sq else None, ws.data_ptr(), nbytes, B, Sq, Skv, H,
                                      D, _dtype_code(q, where), int(bool(causal)), int(window), float(softcap),
@@ -125,7 +125,7 @@ def _attn_snapkv_impl(q, k, v, kernel_size, causal, scale):
   out, score = _attn_score_impl(q, k, v, False, causal, -1, 0.0, scale)
   pooled = torch.empty_like(score)
   dev = q.device
-  with torch.cuda.device(dev):
+  with _on_device(dev):
     st = _lib.load().b200_avg_pool1d_f32(score.data_ptr(), pooled.data_ptr(), score.size(0) * score.size(1),
                                          score.size(2), int(kernel_size), _stream_ptr(dev))
   _lib.check(st, "attn_snapkv_fwd")
@@ -146,7 +146,7 @@ def _attn_corm_impl(q, k, v, causal, scale):
     flags.zero_()
     return out, flags.view(torch.bool)
   ws, nbytes = _workspace(dev, B, Sq, Skv, H)
-  with torch.cuda.device(dev):
+  with _on_device(dev):
     if H != Hk:   # thresholds applied to the group-mean probabilities
       st = _lib.load().b200_attn_score_gqa(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                                            score.data_ptr(), None, flags.data_ptr(), ws.data_ptr(), nbytes, B, Sq,
@@ -194,7 +194,7 @@ def kf_noise_fill(seed, batch, heads, q_len, kv_len, device):
   """kf_noise evaluated by the library's own fill kernel (b200_kf_noise_fill): same tensor, on the GPU."""
   dev = torch.device(device)
   out = torch.empty((batch, heads, q_len, kv_len), dtype=torch.float32, device=dev)
-  with torch.cuda.device(dev):
+  with _on_device(dev):
     st = _lib.load().b200_kf_noise_fill(out.data_ptr(), int(seed) & 0xFFFFFFFFFFFFFFFF, batch, heads, q_len, kv_len,
                                         _stream_ptr(dev))
   _lib.check(st, "kf_noise_fill")
@@ -213,7 +213,7 @@ def _attn_kf_seeded_impl(q, k, v, seed, tau, causal, scale):
   if B == 0 or Sq == 0:
     return out, score.zero_()
   ws, nbytes = _workspace(dev, B, Sq, Skv, H)
-  with torch.cuda.device(dev):
+  with _on_device(dev):
     st = _lib.load().b200_attn_kf_score_seeded(q.data_ptr(), k.data_ptr(), v.data_ptr(),
                                                int(seed) & 0xFFFFFFFFFFFFFFFF, out.data_ptr(), score.data_ptr(),
                                                ws.data_ptr(), nbytes, B, Sq, Skv, H, Hk, D, _dtype_code(q, where),
@@ -237,7 +237,7 @@ def _attn_kf_impl(q, k, v, exp_rand, tau, causal, scale):
   if B == 0 or Sq == 0:
     return out, score.zero_()
   ws, nbytes = _workspace(dev, B, Sq, Skv, H)
-  with torch.cuda.device(dev):
+  with _on_device(dev):
     if H != Hk:   # score of a K/V head = mean over its query heads (figure/membound/attn.py:162-165)
       st = _lib.load().b200_attn_kf_score_gqa(q.data_ptr(), k.data_ptr(), v.data_ptr(), exp_rand.data_ptr(),
                                               out.data_ptr(), score.data_ptr(), ws.data_ptr(), nbytes, B, Sq, Skv, H,
@@ -336,9 +336,19 @@ def _(q, k, v, causal, scale):
 # ----------------------------------------------------------------------------------------------
 # public functions
 # ----------------------------------------------------------------------------------------------
+def _tracing_graph():
+  """True while torch.compile / export traces the caller: only then do the public functions go through the
+  registered custom ops (which carry the fake kernels a tracer needs).  In eager mode they call the implementation
+  directly -- the dispatcher round trip of a Python custom op costs ~17 us of host time per call, more than the
+  kernel takes for a short sequence."""
+  return torch.compiler.is_compiling()
+
+
 @traced
 def attn_fwd(q, k, v, causal=True, window=-1, softcap=0.0, scale=None):
   """softmax(mask(softcap(q k^T * scale))) v   (kernels/attn.py:18-34, kernels/gemma2.py:19-38)."""
+  if not _tracing_graph():
+    return _attn_fwd_impl(q, k, v, causal, window, softcap, scale)
   return _op_attn_fwd(q, k, v, bool(causal), int(window), float(softcap), float(scale or 0.0))
 
 
@@ -352,6 +362,8 @@ def attn_fwd_with_lse(q, k, v, causal=True, window=-1, softcap=0.0, scale=None):
 def attn_score_fwd(q, k, v, want_sq=False, causal=True, window=-1, softcap=0.0, scale=None):
   """Attention output + per-key column sums of the fp32 probabilities (kernels/h2o.py:35-38);
   want_sq adds the column sums of the squared probabilities (kernels/roco.py:42-48)."""
+  if not _tracing_graph():
+    return _attn_score_impl(q, k, v, bool(want_sq), causal, window, softcap, scale)
   op = _op_attn_score_sq_fwd if want_sq else _op_attn_score_fwd
   return op(q, k, v, bool(causal), int(window), float(softcap), float(scale or 0.0))
 
@@ -362,6 +374,10 @@ def attn_kf_fwd(q, k, v, exp_rand=None, tau=1.5, causal=True, scale=None, seed=0
   (kernels/kf.py:36-42).  exp_rand float32 [B, H, Sq, Skv] as the reference passes it -- or None: the kernels then
   generate the noise themselves from `seed` (the tensor kf_noise(seed, ...) describes), and nothing of size
   Sq x Skv is read or stored."""
+  if not _tracing_graph():
+    if exp_rand is None:
+      return _attn_kf_seeded_impl(q, k, v, int(seed), float(tau), causal, scale)
+    return _attn_kf_impl(q, k, v, exp_rand, float(tau), causal, scale)
   if exp_rand is None:
     return _op_attn_kf_seeded_fwd(q, k, v, int(seed), float(tau), bool(causal), float(scale or 0.0))
   return _op_attn_kf_fwd(q, k, v, exp_rand, float(tau), bool(causal), float(scale or 0.0))
@@ -371,6 +387,8 @@ def attn_kf_fwd(q, k, v, exp_rand=None, tau=1.5, causal=True, scale=None, seed=0
 def attn_snapkv_fwd(q, k, v, kernel_size=5, causal=True, scale=None):
   """Attention output + column sums average-pooled over a window of `kernel_size` keys, zero padded
   (kernels/snapkv.py:36-38)."""
+  if not _tracing_graph():
+    return _attn_snapkv_impl(q, k, v, int(kernel_size), causal, scale)
   return _op_attn_snapkv_fwd(q, k, v, int(kernel_size), bool(causal), float(scale or 0.0))
 
 
@@ -378,6 +396,8 @@ def attn_snapkv_fwd(q, k, v, kernel_size=5, causal=True, scale=None):
 def attn_corm_fwd(q, k, v, causal=True, scale=None):
   """Attention output + bool [B, H, Skv]: does any query i attend to the key with probability >= 1 / (i + 1)
   (kernels/corm.py:35-37; the thresholds of Corm.prepare, kernels/corm.py:47-49, are evaluated in the kernel)."""
+  if not _tracing_graph():
+    return _attn_corm_impl(q, k, v, causal, scale)
   return _op_attn_corm_fwd(q, k, v, bool(causal), float(scale or 0.0))
 
 
@@ -398,7 +418,7 @@ def kv_evict_topk(score, k, v, budget, return_indices=False):
     raise ValueError(f"{where}: score shape {tuple(score.shape)} does not match k {tuple(k.shape)}")
   kv_cache = torch.empty((B, 2, int(budget), H, D), dtype=k.dtype, device=dev)
   idx = torch.empty((B, H, int(budget)), dtype=torch.int32, device=dev) if return_indices else None
-  with torch.cuda.device(dev):
+  with _on_device(dev):
     st = _lib.load().b200_kv_evict_topk(score.data_ptr(), k.data_ptr(), v.data_ptr(), kv_cache.data_ptr(),
                                         idx.data_ptr() if return_indices else None, B, S, H, D, int(budget),
                                         _dtype_code(k, where), _stream_ptr(dev))
@@ -426,7 +446,7 @@ def kv_evict_roco(score, score_sq, k, v, q_len, budget, recent, return_indices=F
   keep = int(budget) + int(recent)
   kv_cache = torch.empty((B, 2, keep, H, D), dtype=k.dtype, device=dev)
   idx = torch.empty((B, H, keep), dtype=torch.int32, device=dev) if return_indices else None
-  with torch.cuda.device(dev):
+  with _on_device(dev):
     st = _lib.load().b200_kv_evict_roco(score.data_ptr(), score_sq.data_ptr(), k.data_ptr(), v.data_ptr(),
                                         kv_cache.data_ptr(), idx.data_ptr() if return_indices else None, B, S, H, D,
                                         int(q_len), int(budget), int(recent), _dtype_code(k, where), _stream_ptr(dev))

@@ -8,8 +8,8 @@
 //
 // One to eight CTAs per (batch, head), each of which repeats the (cheap) selection and gathers its share of the
 // rows: the order keys are staged in shared memory once, a 4-pass radix select (8 bits per pass, shared-memory
-// histogram) finds the value of the budget-th largest score, one ordered compaction pass emits the selected key
-// indices already sorted, and the rows are copied with 16-byte accesses.  Ties at the threshold value are
+// histogram) finds the value of the budget-th largest score, one ordered compaction (per-thread key segments, two
+// block scans in all) emits the selected key indices already sorted, and the rows are copied with 16-byte accesses.  Ties at the threshold value are
 // resolved towards the lower key index (torch.topk leaves that choice unspecified).  The selection is a chain of
 // block-wide steps on 16 KB of keys (latency-bound); the gather moves 2 * budget * D elements per head.
 #pragma once
@@ -99,6 +99,39 @@ __device__ __forceinline__ uint32_t block_radix_select(KeyFn key, UseFn use, int
 }
 
 
+// Position of key i inside a shared-memory key array: one padding word per 32 keys, so that both access patterns of
+// the kernels are free of bank conflicts -- consecutive threads on consecutive keys (histogram passes) and thread t on
+// its own contiguous segment of keys (ordered compaction; a segment of 16 keys would otherwise put 16 lanes on one bank).
+__device__ __forceinline__ int skew(int i) { return i + (i >> 5); }
+inline size_t skewed_words(int n) { return (size_t)n + (size_t)(n >> 5) + 1; }
+
+// Ordered compaction.  Thread t owns the contiguous keys [t * K, (t + 1) * K), K = ceil(seq / threads): it counts the
+// keys of its segment that are selected for sure (`sure`) and those that tie at the threshold (`tie`), ONE block-wide
+// scan per count turns them into the number of such keys before the segment, and a second walk over the segment
+// emits every selected key with its final position: (#sure before it) + min(#ties before it, need_tie) -- the first
+// `need_tie` ties in key order are the ones taken.  (The previous form scanned the block once per 256 keys: sixteen
+// scans of two barriers each at 4096 keys, where this one has two.)
+template <class SureFn, class TieFn, class EmitFn>
+__device__ __forceinline__ void ordered_compact(SureFn sure, TieFn tie, EmitFn emit, int seq, int need_tie,
+                                                int* warp_sums) {
+  const int per_thread = (seq + kEvictThreads - 1) / kEvictThreads;
+  const int lo = min(seq, (int)threadIdx.x * per_thread), hi = min(seq, lo + per_thread);
+  int n_sure = 0, n_tie = 0;
+  for (int i = lo; i < hi; ++i) {
+    n_sure += sure(i) ? 1 : 0;
+    n_tie += tie(i) ? 1 : 0;
+  }
+  int total;
+  int sure_before = block_exclusive_scan(n_sure, warp_sums, &total);
+  int tie_before = block_exclusive_scan(n_tie, warp_sums, &total);
+  for (int i = lo; i < hi; ++i) {
+    const bool is_sure = sure(i), is_tie = tie(i);
+    if (is_sure || (is_tie && tie_before < need_tie)) emit(i, sure_before + min(tie_before, need_tie));
+    sure_before += is_sure ? 1 : 0;
+    tie_before += is_tie ? 1 : 0;
+  }
+}
+
 // Gather of the selected rows: kv_cache[b, 0, i, h, :] = k[b, idx_i, h, :], kv_cache[b, 1, i, h, :] = v[b, idx_i, h, :].
 // The CTAs of one (batch, head) -- gridDim.y of them, each of which has made the same selection -- take
 // interleaved slices of the rows; four 16-byte K and V loads are in flight per thread before the first store.
@@ -163,9 +196,9 @@ kv_evict_topk_kernel(const float* __restrict__ score, const uint8_t* __restrict_
   // they cost a shared-memory read instead of a dependent L2 round trip per pass.
   if (staged) {
 #pragma unroll 8
-    for (int i = threadIdx.x; i < seq; i += kEvictThreads) s_keys[i] = score_key(sc[i]);
+    for (int i = threadIdx.x; i < seq; i += kEvictThreads) s_keys[skew(i)] = score_key(sc[i]);
   }
-  auto key_of = [&](int i) { return staged ? s_keys[i] : score_key(sc[i]); };
+  auto key_of = [&](int i) { return staged ? s_keys[skew(i)] : score_key(sc[i]); };
 
   // ---- radix select: key value of the budget-th largest score ----
   int need_equal;
@@ -173,25 +206,12 @@ kv_evict_topk_kernel(const float* __restrict__ score, const uint8_t* __restrict_
                                           &s_remaining, &need_equal);
 
   // ---- ordered compaction: selected indices in ascending order ----
-  // Selected = every key above the threshold plus the first `need_equal` keys equal to it, so the output position
-  // of key i is (#greater before i) + min(#equal before i, need_equal): one block scan of the two counts packed
-  // into one word (greater in the low half, equal in the high half; at most 256 of each per step).
-  int gt_base = 0, eq_base = 0;
-  for (int i0 = 0; i0 < seq; i0 += kEvictThreads) {
-    const int i = i0 + threadIdx.x;
-    const uint32_t u = i < seq ? key_of(i) : 0u;
-    const int is_gt = (i < seq && u > thr) ? 1 : 0;
-    const int is_eq = (i < seq && u == thr) ? 1 : 0;
-    int total;
-    const int before = block_exclusive_scan(is_gt | (is_eq << 16), warp_sums, &total);
-    const int gt_before = gt_base + (before & 0xffff), eq_before = eq_base + (before >> 16);
-    if (is_gt || (is_eq && eq_before < need_equal)) {
-      const int pos = gt_before + min(eq_before, need_equal);
-      if (pos < budget) s_idx[pos] = i;
-    }
-    gt_base += total & 0xffff;
-    eq_base += total >> 16;
-  }
+  // Selected = every key above the threshold plus the first `need_equal` keys equal to it.
+  ordered_compact([&](int i) { return key_of(i) > thr; }, [&](int i) { return key_of(i) == thr; },
+                  [&](int i, int pos) {
+                    if (pos < budget) s_idx[pos] = i;
+                  },
+                  seq, need_equal, warp_sums);
   __syncthreads();
 
   if (indices_out != nullptr && blockIdx.y == 0)
@@ -234,9 +254,10 @@ kv_evict_roco_kernel(const float* __restrict__ score, const float* __restrict__ 
   extern __shared__ int32_t s_dyn[];
   const int keep = budget + recent;
   int32_t* s_idx = s_dyn;                                        // [keep] selected key indices, ascending
-  uint32_t* s_std = reinterpret_cast<uint32_t*>(s_dyn + keep);   // [seq] order keys of std   (when `staged`)
-  uint32_t* s_mean = s_std + (staged ? seq : 0);                 // [seq] order keys of score / q_len
-  uint8_t* in_a = reinterpret_cast<uint8_t*>(s_mean + (staged ? seq : 0));   // [seq] 1 = key belongs to A
+  const int key_words = staged ? seq + (seq >> 5) + 1 : 0;      // padded key arrays (see skew)
+  uint32_t* s_std = reinterpret_cast<uint32_t*>(s_dyn + keep);   // order keys of std   (when `staged`)
+  uint32_t* s_mean = s_std + key_words;                          // order keys of score / q_len
+  uint8_t* in_a = reinterpret_cast<uint8_t*>(s_mean + key_words);   // [seq] 1 = key belongs to A
 
   const int bh = blockIdx.x, b = bh / heads, h = bh - b * heads;
   const float* sc = score + (int64_t)bh * seq;
@@ -245,12 +266,12 @@ kv_evict_roco_kernel(const float* __restrict__ score, const float* __restrict__ 
 #pragma unroll 4
     for (int i = threadIdx.x; i < seq; i += kEvictThreads) {
       const float a = sc[i], a2 = sq[i];
-      s_std[i] = score_key_nan_high(roco_std(a, a2, q_len));
-      s_mean[i] = score_key_nan_high(roco_mean(a, q_len));
+      s_std[skew(i)] = score_key_nan_high(roco_std(a, a2, q_len));
+      s_mean[skew(i)] = score_key_nan_high(roco_mean(a, q_len));
     }
   }
-  auto std_key = [&](int i) { return staged ? s_std[i] : score_key_nan_high(roco_std(sc[i], sq[i], q_len)); };
-  auto mean_key = [&](int i) { return staged ? s_mean[i] : score_key_nan_high(roco_mean(sc[i], q_len)); };
+  auto std_key = [&](int i) { return staged ? s_std[skew(i)] : score_key_nan_high(roco_std(sc[i], sq[i], q_len)); };
+  auto mean_key = [&](int i) { return staged ? s_mean[skew(i)] : score_key_nan_high(roco_mean(sc[i], q_len)); };
 
   // ---- A: the `recent` keys with the largest std (ties towards the lower index) ----
   for (int i = threadIdx.x; i < seq; i += kEvictThreads) in_a[i] = 0;
@@ -258,16 +279,9 @@ kv_evict_roco_kernel(const float* __restrict__ score, const float* __restrict__ 
     int need_eq;
     const uint32_t thr = block_radix_select(std_key, [](int) { return true; }, seq, recent, hist, warp_sums,
                                             &s_prefix, &s_remaining, &need_eq);
-    int eq_base = 0;
-    for (int i0 = 0; i0 < seq; i0 += kEvictThreads) {
-      const int i = i0 + threadIdx.x;
-      const uint32_t u = i < seq ? std_key(i) : 0u;
-      const int is_eq = (i < seq && u == thr) ? 1 : 0;
-      int eq_total;
-      const int eq_before = eq_base + block_exclusive_scan(is_eq, warp_sums, &eq_total);
-      if (i < seq && (u > thr || (is_eq && eq_before < need_eq))) in_a[i] = 1;
-      eq_base += eq_total;
-    }
+    __syncthreads();   // in_a cleared by all threads before any thread marks its segment
+    ordered_compact([&](int i) { return std_key(i) > thr; }, [&](int i) { return std_key(i) == thr; },
+                    [&](int i, int) { in_a[i] = 1; }, seq, need_eq, warp_sums);
   }
   __syncthreads();
 
@@ -279,26 +293,13 @@ kv_evict_roco_kernel(const float* __restrict__ score, const float* __restrict__ 
                                &s_prefix, &s_remaining, &need_eq_b);
 
   // ---- ordered compaction of A u B ----
-  // "sure" keys (in A, or above the B threshold) and keys equal to the B threshold are counted in one packed scan;
-  // position of key i = (#sure before i) + min(#equal before i, need_eq_b), as in the top-k kernel
-  int sure_base = 0, eq_base = 0;
-  for (int i0 = 0; i0 < seq; i0 += kEvictThreads) {
-    const int i = i0 + threadIdx.x;
-    const bool a = i < seq && in_a[i] != 0;
-    const bool cand = i < seq && !a && budget > 0;
-    const uint32_t u = cand ? mean_key(i) : 0u;
-    const int is_sure = (a || (cand && u > thr_b)) ? 1 : 0;
-    const int is_eq = (cand && u == thr_b) ? 1 : 0;
-    int total;
-    const int before = block_exclusive_scan(is_sure | (is_eq << 16), warp_sums, &total);
-    const int sure_before = sure_base + (before & 0xffff), eq_before = eq_base + (before >> 16);
-    if (is_sure || (is_eq && eq_before < need_eq_b)) {
-      const int pos = sure_before + min(eq_before, need_eq_b);
-      if (pos < keep) s_idx[pos] = i;
-    }
-    sure_base += total & 0xffff;
-    eq_base += total >> 16;
-  }
+  // "sure" keys (in A, or above the B threshold) and the first need_eq_b keys that tie at the B threshold
+  ordered_compact([&](int i) { return in_a[i] != 0 || (budget > 0 && mean_key(i) > thr_b); },
+                  [&](int i) { return in_a[i] == 0 && budget > 0 && mean_key(i) == thr_b; },
+                  [&](int i, int pos) {
+                    if (pos < keep) s_idx[pos] = i;
+                  },
+                  seq, need_eq_b, warp_sums);
   __syncthreads();
 
   if (indices_out != nullptr && blockIdx.y == 0)
@@ -360,8 +361,9 @@ inline int kv_evict_roco_impl(const float* score, const float* score_sq, const v
     return B200_ERR_MISALIGNED;
   const size_t smem_min = (size_t)(budget + recent) * sizeof(int32_t) + (size_t)((seq + 15) / 16) * 16;
   if (smem_min > 200 * 1024) return B200_ERR_UNSUPPORTED;
-  const int staged = smem_min + (size_t)seq * 8 <= 200 * 1024 ? 1 : 0;
-  const size_t smem = smem_min + (staged ? (size_t)seq * 8 : 0);
+  const size_t key_bytes = 2 * skewed_words(seq) * sizeof(uint32_t);   // std and mean keys, padded
+  const int staged = smem_min + key_bytes <= 200 * 1024 ? 1 : 0;
+  const size_t smem = smem_min + (staged ? key_bytes : 0);
   const dim3 grid(batch * heads, evict_ctas_per_head(batch * heads));
   return elem_bytes == 2
              ? launch_kv_evict_roco<2>(grid, smem, stream, score, score_sq, k, v, kv_cache, indices, seq, heads,
@@ -381,8 +383,9 @@ inline int kv_evict_topk_impl(const float* score, const void* k, const void* v, 
     return B200_ERR_MISALIGNED;
   if (budget > 12288) return B200_ERR_UNSUPPORTED;   // index list lives in shared memory (48 KB)
   const size_t smem_idx = (size_t)budget * sizeof(int32_t);
-  const int staged = smem_idx + (size_t)seq * 4 <= 200 * 1024 ? 1 : 0;
-  const size_t smem = smem_idx + (staged ? (size_t)seq * 4 : 0);
+  const size_t key_bytes = skewed_words(seq) * sizeof(uint32_t);   // padded key array
+  const int staged = smem_idx + key_bytes <= 200 * 1024 ? 1 : 0;
+  const size_t smem = smem_idx + (staged ? key_bytes : 0);
   const dim3 grid(batch * heads, evict_ctas_per_head(batch * heads));
   return elem_bytes == 2 ? launch_kv_evict_topk<2>(grid, smem, stream, score, k, v, kv_cache, indices, seq, heads,
                                                    head_dim, budget, staged)

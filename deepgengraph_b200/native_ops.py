@@ -42,6 +42,29 @@ def _stream_ptr(dev):
   return torch.cuda.current_stream(dev).cuda_stream
 
 
+class _on_device:
+  """`with _on_device(dev):` makes `dev` the current CUDA device for the enclosed library call.  When it already is
+  (the usual case: one process per GPU) nothing is switched -- torch.cuda.device costs several microseconds per
+  entry, which is as much host time as a whole launch."""
+  __slots__ = ("dev", "ctx")
+
+  def __init__(self, dev):
+    self.dev = dev
+    self.ctx = None
+
+  def __enter__(self):
+    idx = self.dev.index
+    if idx is not None and idx != torch.cuda.current_device():
+      self.ctx = torch.cuda.device(self.dev)
+      self.ctx.__enter__()
+    return self
+
+  def __exit__(self, *exc):
+    if self.ctx is not None:
+      return self.ctx.__exit__(*exc)
+    return False
+
+
 @traced
 def rms_norm(out, input, weight, epsilon):
   """out = T(input * rsqrt(mean(input^2, -1) + epsilon)) * weight   (csrc/norm.cu:34-56)."""
@@ -55,7 +78,7 @@ def rms_norm(out, input, weight, epsilon):
   if not (out.is_contiguous() and input.is_contiguous() and weight.is_contiguous()):
     raise ValueError(f"{where}: tensors must be contiguous")
   tokens = input.numel() // hidden if hidden else 0
-  with torch.cuda.device(dev):
+  with _on_device(dev):
     st = _lib.load().b200_rms_norm(out.data_ptr(), input.data_ptr(), weight.data_ptr(), float(epsilon), tokens,
                                    hidden, _dtype_code(input, where), _stream_ptr(dev))
   _lib.check(st, where)
@@ -74,7 +97,7 @@ def fused_add_rms_norm(input, residual, weight, epsilon):
   if not (residual.is_contiguous() and input.is_contiguous() and weight.is_contiguous()):
     raise ValueError(f"{where}: tensors must be contiguous")
   tokens = input.numel() // hidden if hidden else 0
-  with torch.cuda.device(dev):
+  with _on_device(dev):
     st = _lib.load().b200_fused_add_rms_norm(input.data_ptr(), residual.data_ptr(), weight.data_ptr(),
                                              float(epsilon), tokens, hidden, _dtype_code(input, where),
                                              _stream_ptr(dev))
@@ -91,7 +114,7 @@ def _act_and_mul(fn_name, out, input):
   if not (out.is_contiguous() and input.is_contiguous()):
     raise ValueError(f"{fn_name}: tensors must be contiguous")
   tokens = input.numel() // (2 * d) if d else 0
-  with torch.cuda.device(dev):
+  with _on_device(dev):
     st = getattr(_lib.load(), "b200_" + fn_name)(out.data_ptr(), input.data_ptr(), tokens, d,
                                                  _dtype_code(input, fn_name), _stream_ptr(dev))
   _lib.check(st, fn_name)
@@ -133,7 +156,7 @@ def rotary_embedding_online(positions, query, key, head_size, rope_theta):
     flat = t.reshape(-1, t.size(-1)) if t.dim() > 2 else t
     if flat.data_ptr() != t.data_ptr() or (flat.size(0) > 1 and flat.stride(0) != t.stride(-2)):
       raise ValueError(f"{where}: {name} rows are not uniformly strided")
-  with torch.cuda.device(dev):
+  with _on_device(dev):
     st = _lib.load().b200_rotary_embedding_online(
         positions.data_ptr(), query.data_ptr(), key.data_ptr(), tokens, query.size(-1) // head_size,
         key.size(-1) // head_size, int(head_size), query.stride(-2), key.stride(-2), float(rope_theta),

@@ -102,10 +102,11 @@ def test_vectors_too_long_for_shared_memory_staging(cuda_device):
   assert torch.equal(idx.cpu().long(), ref_idx) and torch.equal(cache.cpu(), ref_cache)
 
 
-@pytest.mark.parametrize("seq,budget", [(12000, 100), (12032, 12), (39936, 12288), (50000, 12288)])
+@pytest.mark.parametrize("seq,budget", [(11500, 100), (11600, 12), (11700, 300), (12000, 100), (39936, 12288), (50000, 12288)])
 def test_shared_memory_sizes_around_the_opt_in_threshold(cuda_device, seq, budget):
-  # dynamic shared memory = 4 * budget (+ 4 * seq while the keys fit): 48 400 B, 48 176 B (just under 48 KB, where the
-  # static arrays push the total over the default limit), 208 896 B -> unstaged 49 152 B, and the unstaged maximum
+  # dynamic shared memory = 4 * budget (+ the padded key array while it fits): sizes just below and just above the
+  # 48 KB default limit (which static and dynamic shared memory share), the largest budget with the keys left in
+  # global memory, and a sequence beyond what shared memory can stage
   g = torch.Generator().manual_seed(seq + budget)
   score = torch.rand(1, 1, seq, generator=g)
   k = torch.randn(1, seq, 1, 64, generator=g).to(torch.bfloat16)
