@@ -208,8 +208,8 @@ int b200_gelu_tanh_and_mul(void* out, const void* input, int64_t num_tokens, int
   cudaStream_t s = (cudaStream_t)stream;
   switch (dtype) {
     case B200_F32: return launch_act_and_mul<float, GeluTanhOp>(out, input, num_tokens, d, s);
-    case B200_F16: return launch_act_and_mul<__half, GeluTanhOp>(out, input, num_tokens, d, s);
-    case B200_BF16: return launch_act_and_mul<__nv_bfloat16, GeluTanhOp>(out, input, num_tokens, d, s);
+    case B200_F16: return launch_act_and_mul<__half, GeluTanhOpT<false>>(out, input, num_tokens, d, s);
+    case B200_BF16: return launch_act_and_mul<__nv_bfloat16, GeluTanhOpT<false>>(out, input, num_tokens, d, s);
     default: return B200_ERR_BAD_DTYPE;
   }
 }

@@ -271,33 +271,73 @@ int launch_rms_norm(void* out, void* input, void* residual, const void* weight, 
 struct SiluOp {
   __device__ __forceinline__ float operator()(float x) const { return x / (1.0f + __expf(-x)); }
 };
-struct GeluTanhOp {
+// ACCURATE = true (fp32 tensors): tanh(u) = 1 - 2 / (1 + e^{2u}), spelled out because fast-math maps tanhf to the
+// hardware approximation.  ACCURATE = false (16-bit tensors): tanh.approx.f32 itself -- its error (~5e-4 absolute)
+// is a quarter of a bf16 ulp of the result and halves the special-function work of the kernel.
+template <bool ACCURATE>
+struct GeluTanhOpT {
   __device__ __forceinline__ float operator()(float x) const {
     const float kAlpha = 0.7978845608028654f;  // sqrt(2/pi)
     const float inner = kAlpha * (x + 0.044715f * x * x * x);
-    // tanh(u) = 1 - 2 / (1 + e^{2u}); spelled out because fast-math maps tanhf to the ~5e-4 approximation
-    const float t = 1.0f - 2.0f / (1.0f + __expf(2.0f * inner));
+    const float t = ACCURATE ? 1.0f - 2.0f / (1.0f + __expf(2.0f * inner)) : tanh_approx(inner);
     return 0.5f * x * (1.0f + t);
   }
 };
+using GeluTanhOp = GeluTanhOpT<true>;
 
+// out = T(act(x)) * y for one 16-byte vector (csrc/activation.cu:6-22: the activation is rounded to T, the product is
+// taken in T).  16-bit types: the product is one packed multiply on the raw y pairs (a single rounding, like the fp32
+// product rounded once).
 template <typename T, typename Op>
+__device__ __forceinline__ uint4 act_round_mul(const uint4& x_raw, const uint4& y_raw) {
+  constexpr int VN = 16 / sizeof(T);
+  Op op;
+  float x[VN];
+  unpack16<T>(x_raw, x);
+  uint4 out;
+  if constexpr (sizeof(T) == 4) {
+    const float* y = reinterpret_cast<const float*>(&y_raw);
+    float* o = reinterpret_cast<float*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = op(x[i]) * y[i];
+  } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    const __nv_bfloat162* y2 = reinterpret_cast<const __nv_bfloat162*>(&y_raw);
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o2[i] = __hmul2(__floats2bfloat162_rn(op(x[2 * i]), op(x[2 * i + 1])), y2[i]);
+  } else {
+    const __half2* y2 = reinterpret_cast<const __half2*>(&y_raw);
+    __half2* o2 = reinterpret_cast<__half2*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o2[i] = __hmul2(__floats2half2_rn(op(x[2 * i]), op(x[2 * i + 1])), y2[i]);
+  }
+  return out;
+}
+
+// Index = int when the vector count fits 31 bits (a 64-bit division per vector costs more than the activation)
+template <typename T, typename Op, typename Index>
 __global__ void __launch_bounds__(256)
 act_and_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ in, int64_t num_tokens, int d) {
   constexpr int VN = 16 / sizeof(T);
-  const int vec_per_row = d / VN;
-  const int64_t total = num_tokens * vec_per_row;
-  Op op;
-  for (int64_t g = (int64_t)blockIdx.x * 256 + threadIdx.x; g < total; g += (int64_t)gridDim.x * 256) {
-    const int64_t t = g / vec_per_row;
-    const int c = (int)(g - t * vec_per_row);
-    const T* xrow = in + t * 2 * (int64_t)d;
-    float x[VN], y[VN], r[VN];
-    unpack16<T>(ld_nc_16(xrow + (int64_t)c * VN), x);
-    unpack16<T>(ld_nc_16(xrow + d + (int64_t)c * VN), y);
-#pragma unroll
-    for (int i = 0; i < VN; ++i) r[i] = to_f32<T>(from_f32<T>(op(x[i]))) * y[i];
-    st_16(out + t * (int64_t)d + (int64_t)c * VN, pack16<T>(r));
+  const Index vec_per_row = (Index)(d / VN);
+  const Index total = (Index)num_tokens * vec_per_row;
+  const Index step = (Index)gridDim.x * 256;
+  // two vectors per thread and step: four 16-byte loads in flight before the first store
+  for (Index g = (Index)blockIdx.x * 256 + threadIdx.x; g < total; g += 2 * step) {
+    const Index g1 = g + step;
+    const Index t0 = g / vec_per_row, t1 = g1 / vec_per_row;
+    const Index c0 = g - t0 * vec_per_row, c1 = g1 - t1 * vec_per_row;
+    const T* x0 = in + (int64_t)t0 * 2 * d + (int64_t)c0 * VN;
+    const T* x1 = in + (int64_t)t1 * 2 * d + (int64_t)c1 * VN;
+    const bool two = g1 < total;
+    const uint4 a0 = ld_nc_16(x0), b0 = ld_nc_16(x0 + d);
+    uint4 a1 = a0, b1 = b0;
+    if (two) {
+      a1 = ld_nc_16(x1);
+      b1 = ld_nc_16(x1 + d);
+    }
+    st_16(out + (int64_t)t0 * d + (int64_t)c0 * VN, act_round_mul<T, Op>(a0, b0));
+    if (two) st_16(out + (int64_t)t1 * d + (int64_t)c1 * VN, act_round_mul<T, Op>(a1, b1));
   }
 }
 
@@ -322,8 +362,11 @@ int launch_act_and_mul(void* out, const void* in, int64_t num_tokens, int d, cud
   const bool vec_ok = (d % VN == 0) && aligned16(out) && aligned16(in);
   if (vec_ok) {
     const int64_t total = num_tokens * (d / VN);
-    const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((total + 255) / 256, (int64_t)sms * 16));
-    act_and_mul_vec_kernel<T, Op><<<grid, 256, 0, stream>>>((T*)out, (const T*)in, num_tokens, d);
+    const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((total + 511) / 512, (int64_t)sms * 16));
+    if (total + 2 * (int64_t)grid * 256 < (int64_t)1 << 31)
+      act_and_mul_vec_kernel<T, Op, int><<<grid, 256, 0, stream>>>((T*)out, (const T*)in, num_tokens, d);
+    else
+      act_and_mul_vec_kernel<T, Op, int64_t><<<grid, 256, 0, stream>>>((T*)out, (const T*)in, num_tokens, d);
   } else {
     const int64_t total = num_tokens * d;
     const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((total + 255) / 256, (int64_t)sms * 16));
