@@ -133,7 +133,8 @@ struct SweepCfg {
   static constexpr int THREADS = (COMPUTE_WARPS + 2) * 32;   // + TMA producer warp + MMA issuer warp
   // launch bound (registers): two CTAs share an SM -- the 320-thread column-sum CTAs and the KeyFormer CTAs
   static constexpr int CTAS_PER_SM = (CWG == 2 || MODE != SWEEP_COLSUM) ? 2 : 1;
-  static_assert(CWG == 1 || (CWG == 2 && BX == 128 && !A_TMEM), "two compute warpgroups: 128-wide blocks only");
+  static_assert(CWG == 1 || CWG == 2, "one or two compute warpgroups");
+  static_assert(BX / 32 % CWG == 0, "every compute warpgroup takes whole 32-column chunks");
   static constexpr int BAR_A_FULL = 0;
   static constexpr int BAR_X_FULL = 1;
   static constexpr int BAR_X_EMPTY = BAR_X_FULL + STAGES;
@@ -559,6 +560,10 @@ __device__ __forceinline__ void sweep_compute_rowlse(const SweepCtx<Cfg>& c, con
   const float cz = p.scale_log2 * p.inv_tau;
   float m = -1.0e30f, l = 0.f;
   const int hi_key = p.causal ? min(row + p.delta, p.kv_len - 1) : p.kv_len - 1;
+  // with two compute warpgroups each takes half of the block's key columns: a row's running (maximum, sum) is then
+  // split over two threads and merged once at the end
+  constexpr int NCH = BX / 32 / Cfg::CWG;
+  const int ch0 = Cfg::CWG == 2 ? (int)(threadIdx.x >> 7) * NCH : 0;
 
   for (int blk = c.blk_lo; blk < c.blk_hi; ++blk) {
     const int n = blk - c.blk_lo, st = n % ST, tb = n & 1;
@@ -568,10 +573,11 @@ __device__ __forceinline__ void sweep_compute_rowlse(const SweepCtx<Cfg>& c, con
     tc_fence_after();
     [[maybe_unused]] const uint8_t* nst = c.sN + st * Cfg::N_STAGE_STRIDE;
     const int hi_c = hi_key - blk * BX;
-    float z[BX];
+    float z[NCH * 32];
     float mx = -INFINITY;
 #pragma unroll
-    for (int ch = 0; ch < BX / 32; ++ch) {
+    for (int cc = 0; cc < NCH; ++cc) {
+      const int ch = ch0 + cc;
       uint32_t sr[32];
       tmem_ld32(lane_addr + tb * BX + ch * 32, sr);
       tmem_ld_wait();
@@ -594,7 +600,7 @@ __device__ __forceinline__ void sweep_compute_rowlse(const SweepCtx<Cfg>& c, con
           const int col = ch * 32 + q4 * 4 + u;
           float v = fmaf(__uint_as_float(sr[q4 * 4 + u]), cz, -lg[u] * p.inv_tau);
           if (col > hi_c) v = -INFINITY;
-          z[col] = v;
+          z[cc * 32 + q4 * 4 + u] = v;
           mx = fmaxf(mx, v);
         }
       }
@@ -608,12 +614,27 @@ __device__ __forceinline__ void sweep_compute_rowlse(const SweepCtx<Cfg>& c, con
     const float m_new = fmaxf(m, mx);
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-    for (int i = 0; i < BX; i += 2) {
+    for (int i = 0; i < NCH * 32; i += 2) {
       s0 += ex2_approx(z[i] - m_new);
       s1 += ex2_approx(z[i + 1] - m_new);
     }
     l = l * ex2_approx(m - m_new) + (s0 + s1);
     m = m_new;
+  }
+  if constexpr (Cfg::CWG == 2) {
+    // merge the two halves of every row: (m, l) of the second warpgroup goes through shared memory
+    if (threadIdx.x >= 128) {
+      c.sCombine[r_local] = m;
+      c.sCombine[128 + r_local] = l;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&c.bars[Cfg::BAR_COMBINE]);
+      return;
+    }
+    if (!mbar_wait(&c.bars[Cfg::BAR_COMBINE], 0, c.abort_flag, WAIT_T_FULL)) return;
+    const float m1 = c.sCombine[r_local], l1 = c.sCombine[128 + r_local];
+    const float mm = fmaxf(m, m1);
+    l = l * ex2_approx(m - mm) + l1 * ex2_approx(m1 - mm);
+    m = mm;
   }
   if (row < p.q_len) p.lse_out[(int64_t)c.bh * p.lse_stride + row] = m + log2f(l);
 }
@@ -711,7 +732,7 @@ attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   c.tmem_base = *tmem_slot;
 
   if (warp < CW) {
-    if constexpr (Cfg::A_TMEM) {
+    if constexpr (Cfg::A_TMEM) if (warp < 4) {
       // thread r copies row r of the stationary tile (256 contiguous bytes) from global memory into TMEM lane r;
       // a 32-bit TMEM column holds two consecutive 16-bit elements, which is the order they have in memory
       const int row = c.a0 + (int)threadIdx.x;
@@ -817,7 +838,10 @@ constexpr int kSweepChunkBlocks = B200_SWEEP_CHUNK;
 #ifndef B200_KF_STAGES
 #define B200_KF_STAGES 2
 #endif
-// compute warpgroups of the plain column-sum sweep (see SweepCfg)
+// compute warpgroups of the KeyFormer sweeps and of the plain column-sum sweep (see SweepCfg)
+#ifndef B200_KF_CWG
+#define B200_KF_CWG 2
+#endif
 #ifndef B200_COLSUM_CWG
 #define B200_COLSUM_CWG (B200_COLSUM_BX == 128 ? 2 : 1)
 #endif
@@ -1093,7 +1117,7 @@ inline int attn_kf_impl(const void* q, const void* k, const void* v, const float
   p.a_rows = q_len;
   p.a_heads = heads;
 #define B200_KF_SWEEP(MODE_, BF, GEN_, TA, TX, TN, NC, NT) \
-  launch_sweep<MODE_, 64, B200_KF_STAGES, BF, false, AUX_NONE, false, 1, GEN_>(TA, TX, TN, p, NC, NT, stream)
+  launch_sweep<MODE_, 64, B200_KF_STAGES, BF, false, AUX_NONE, false, B200_KF_CWG, GEN_>(TA, TX, TN, p, NC, NT, stream)
   if (gen)
     rc = bf16 ? B200_KF_SWEEP(SWEEP_KF_ROWLSE, true, true, tq128, tk64, tn_rows128, 1, q_tiles)
               : B200_KF_SWEEP(SWEEP_KF_ROWLSE, false, true, tq128, tk64, tn_rows128, 1, q_tiles);
