@@ -344,7 +344,11 @@ __device__ __forceinline__ bool fwd_softmax_block(const FwdCtx<Cfg, BF16>& c, co
   tmem_ld_wait();
   if (tl_on) B200_TL(tl_base + 1);
 
+  // Row maximum of the block.  With a soft-cap the capped logit is a monotone function of the raw one, so the
+  // maximum is taken over the RAW values (no special-function work in this pass) and capped once; the pass also
+  // finds the largest |raw| so that the warp can vote for the polynomial-only exponential pass below.
   float mx0 = -INFINITY, mx1 = -INFINITY;
+  [[maybe_unused]] float ab0 = 0.f, ab1 = 0.f;
 #pragma unroll
   for (int ch = 0; ch < BN / 32; ++ch) {
 #pragma unroll
@@ -353,19 +357,33 @@ __device__ __forceinline__ bool fwd_softmax_block(const FwdCtx<Cfg, BF16>& c, co
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         float s = __uint_as_float(sr[ch][i + u]);
-        if constexpr (SOFTCAP) s = tanh_approx(s * p.cap_in);   // cap_out is folded into cmul
+        [[maybe_unused]] float sa = fabsf(s);
         if constexpr (MASK) {
           const int col = ch * 32 + i + u;
-          if (col > hi_c || col < lo_c) s = -INFINITY;
+          if (col > hi_c || col < lo_c) {
+            s = -INFINITY;
+            sa = 0.f;
+          }
+          // (with a soft-cap the registers keep the raw value: the exponential pass masks by column again)
+          if constexpr (!SOFTCAP) sr[ch][i + u] = __float_as_uint(s);
         }
-        if constexpr (SOFTCAP || MASK) sr[ch][i + u] = __float_as_uint(s);
         v[u] = s;
+        if constexpr (SOFTCAP) {
+          if (u < 2) ab0 = fmaxf(ab0, sa); else ab1 = fmaxf(ab1, sa);
+        }
       }
       mx0 = fmax3(mx0, v[0], v[1]);
       mx1 = fmax3(mx1, v[2], v[3]);
     }
   }
-  const float m_blk = fmaxf(mx0, mx1) * cmul;  // -inf when the whole row is masked inside this block
+  float m_blk = fmaxf(mx0, mx1);   // -inf when the whole row is masked inside this block
+  [[maybe_unused]] bool cap_poly_only = false;
+  if constexpr (SOFTCAP) {
+    m_blk = m_blk == -INFINITY ? -INFINITY : softcap_tanh(m_blk * p.cap_in) * cmul;   // cap_out is folded into cmul
+    cap_poly_only = !__any_sync(0xffffffffu, fmaxf(ab0, ab1) * p.cap_in > kCapPolyMax);
+  } else {
+    m_blk *= cmul;
+  }
   if (tl_on) B200_TL(tl_base + 2);
   float alpha = 1.0f;
   bool rescale = false;
@@ -411,30 +429,66 @@ __device__ __forceinline__ bool fwd_softmax_block(const FwdCtx<Cfg, BF16>& c, co
   // P = exp2(x - m), packed to the 16-bit input type, written over the first BN/2 columns of S
   const float2 c2 = make_float2(cmul, cmul), nm2 = make_float2(-m, -m);
   float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
-#pragma unroll
-  for (int ch = 0; ch < BN / 32; ++ch) {
-    uint32_t pk[16];
-#pragma unroll
-    for (int i = 0; i < 32; i += 4) {
-      float2 x0 = ffma2(make_float2(__uint_as_float(sr[ch][i + 0]), __uint_as_float(sr[ch][i + 1])), c2, nm2);
-      float2 x1 = ffma2(make_float2(__uint_as_float(sr[ch][i + 2]), __uint_as_float(sr[ch][i + 3])), c2, nm2);
-      // masked blocks hold -inf entries and stay on the special-function unit; elsewhere a fixed, interleaved
-      // subset of the column groups goes through the polynomial
-      if (!MASK && (((i / 4) * kPolyOf8) % 8) < kPolyOf8) {
-        x0 = exp2_poly2(x0);
-        x1 = exp2_poly2(x1);
+  // x = logit - m in base-2 units for four columns; POLY_ONLY: every |raw / cap| of the warp's block is <= 1
+  auto exponents = [&](auto poly_only_tag, int ch, int i, float2& x0, float2& x1) {
+    const float2 s0 = make_float2(__uint_as_float(sr[ch][i + 0]), __uint_as_float(sr[ch][i + 1]));
+    const float2 s1 = make_float2(__uint_as_float(sr[ch][i + 2]), __uint_as_float(sr[ch][i + 3]));
+    if constexpr (SOFTCAP) {
+      const float2 a2 = make_float2(p.cap_in, p.cap_in);
+      const float2 y0 = fmul2(s0, a2), y1 = fmul2(s1, a2);
+      if constexpr (decltype(poly_only_tag)::value) {
+        x0 = ffma2(y0, softcap_r2(y0, cmul), nm2);
+        x1 = ffma2(y1, softcap_r2(y1, cmul), nm2);
       } else {
-        x0.x = ex2_approx(x0.x);
-        x0.y = ex2_approx(x0.y);
-        x1.x = ex2_approx(x1.x);
-        x1.y = ex2_approx(x1.y);
+        x0 = ffma2(make_float2(softcap_tanh(y0.x), softcap_tanh(y0.y)), c2, nm2);
+        x1 = ffma2(make_float2(softcap_tanh(y1.x), softcap_tanh(y1.y)), c2, nm2);
       }
-      acc0 = fadd2(acc0, x0);
-      acc1 = fadd2(acc1, x1);
-      pk[i / 2] = pack2<BF16>(x0.x, x0.y);
-      pk[i / 2 + 1] = pack2<BF16>(x1.x, x1.y);
+      if constexpr (MASK) {
+        const int col = ch * 32 + i;
+        if (col + 0 > hi_c || col + 0 < lo_c) x0.x = -INFINITY;
+        if (col + 1 > hi_c || col + 1 < lo_c) x0.y = -INFINITY;
+        if (col + 2 > hi_c || col + 2 < lo_c) x1.x = -INFINITY;
+        if (col + 3 > hi_c || col + 3 < lo_c) x1.y = -INFINITY;
+      }
+    } else {
+      x0 = ffma2(s0, c2, nm2);
+      x1 = ffma2(s1, c2, nm2);
     }
-    tmem_st16(s_addr + ch * 16, pk);
+  };
+  auto exp_pass = [&](auto poly_only_tag) {
+#pragma unroll
+    for (int ch = 0; ch < BN / 32; ++ch) {
+      uint32_t pk[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        float2 x0, x1;
+        exponents(poly_only_tag, ch, i, x0, x1);
+        // masked blocks hold -inf entries and stay on the special-function unit; elsewhere a fixed, interleaved
+        // subset of the column groups goes through the polynomial
+        if (!MASK && (((i / 4) * kPolyOf8) % 8) < kPolyOf8) {
+          x0 = exp2_poly2(x0);
+          x1 = exp2_poly2(x1);
+        } else {
+          x0.x = ex2_approx(x0.x);
+          x0.y = ex2_approx(x0.y);
+          x1.x = ex2_approx(x1.x);
+          x1.y = ex2_approx(x1.y);
+        }
+        acc0 = fadd2(acc0, x0);
+        acc1 = fadd2(acc1, x1);
+        pk[i / 2] = pack2<BF16>(x0.x, x0.y);
+        pk[i / 2 + 1] = pack2<BF16>(x1.x, x1.y);
+      }
+      tmem_st16(s_addr + ch * 16, pk);
+    }
+  };
+  if constexpr (SOFTCAP) {
+    if (cap_poly_only)
+      exp_pass(std::true_type{});
+    else
+      exp_pass(std::false_type{});
+  } else {
+    exp_pass(std::false_type{});
   }
   l += (acc0.x + acc0.y) + (acc1.x + acc1.y);
   if (turn_pass != nullptr) {

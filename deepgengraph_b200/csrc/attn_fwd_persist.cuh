@@ -55,23 +55,41 @@ __device__ __forceinline__ TileInfo decode_item(int item, const FwdParams& p, co
   return t;
 }
 
-template <int D_>
-struct PersistCfg : FwdCfg<D_, 64, 1, 2> {
-  using Base = FwdCfg<D_, 64, 1, 2>;
+// Q as the TMEM-resident A operand of S = Q K^T (0 = both operands in shared memory) and the S buffers that
+// then fit: head_dim 128 shares the SM between two CTAs (256 columns each: S 64 + Q 64 + O 128), head_dim 256
+// has the SM to itself (S 2 x 64 + Q 128 + O 256 = 512).
+#ifndef B200_FWD_QT128
+#define B200_FWD_QT128 0
+#endif
+#ifndef B200_FWD_QT256
+#define B200_FWD_QT256 1
+#endif
+
+template <int D_, bool QT_ = (D_ == 128 ? B200_FWD_QT128 : B200_FWD_QT256) != 0>
+struct PersistCfg : FwdCfg<D_, 64, 1, (QT_ && D_ == 128) ? 1 : 2> {
+  using Base = FwdCfg<D_, 64, 1, (QT_ && D_ == 128) ? 1 : 2>;
+  static constexpr bool QT = QT_;
+  static constexpr int Q_COL = Base::SB * Base::BN;   // first TMEM column of the Q operand
+  static_assert(!QT || (Q_COL + D_ / 2 <= Base::O_BASE && Base::TMEM_USED <= Base::TMEM_COLS), "TMEM plan");
+  static constexpr int SOFTMAX_WARPS = 4;
+  static constexpr int THREADS_P = (SOFTMAX_WARPS + 2) * 32;
   static constexpr int BAR_SCHED = Base::NUM_BARS;        // [2] tile descriptor slot k % 2 published
   static constexpr int BAR_Q_FREE = BAR_SCHED + 2;        // last S MMA of a tile retired: Q buffer reusable
-  static constexpr int BAR_SCHED_FREE = BAR_Q_FREE + 1;   // [2] descriptor slot read by all five consumers
-  static constexpr int NUM_BARS_P = BAR_SCHED_FREE + 2;
+  static constexpr int BAR_SCHED_FREE = BAR_Q_FREE + 1;   // [2] descriptor slot read by all its consumers
+  static constexpr int BAR_QT_FULL = BAR_SCHED_FREE + 2;  // Q operand of the tile is in TMEM
+  static constexpr int NUM_BARS_P = BAR_QT_FULL + 1;
   static constexpr int SMEM_BYTES_P = Base::SMEM_TILES + NUM_BARS_P * 8 + 64 + 1024;
   static_assert(SMEM_BYTES_P <= Base::SMEM_BUDGET, "shared memory budget exceeded");
 };
 
 template <int D_, bool BF16, bool SOFTCAP>
-__global__ void __launch_bounds__(192, PersistCfg<D_>::CTAS_PER_SM)
+__global__ void __launch_bounds__(PersistCfg<D_>::THREADS_P, PersistCfg<D_>::CTAS_PER_SM)
 attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                         const __grid_constant__ CUtensorMap tm_v, const FwdParams p, const SchedParams sp) {
   using Cfg = PersistCfg<D_>;
   constexpr int SL = Cfg::SLOTS, D = Cfg::D, BN = Cfg::BN, BM = Cfg::BM, SB = Cfg::SB;
+  constexpr int PRODUCER_WARP = Cfg::SOFTMAX_WARPS;
+  constexpr bool QT = Cfg::QT;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
@@ -95,14 +113,17 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   if (threadIdx.x == 0) {
 #pragma unroll
     for (int i = 0; i < Cfg::NUM_BARS_P; ++i) {
-      const bool is_p_full = (i >= Cfg::BAR_P_FULL && i < Cfg::BAR_P_FULL + SB);   // 4 softmax warps
+      const bool is_p_full = (i >= Cfg::BAR_P_FULL && i < Cfg::BAR_P_FULL + SB);   // every softmax warp
       const bool is_sched_free = (i >= Cfg::BAR_SCHED_FREE && i < Cfg::BAR_SCHED_FREE + 2);   // + the MMA issuer
-      mbar_init(&c.bars[i], is_sched_free ? 5u : is_p_full ? 4u : 1u);
+      // with Q in TMEM the softmax warps fill it from the shared-memory tile and release that tile themselves
+      const bool is_q_copy = QT && (i == Cfg::BAR_QT_FULL || i == Cfg::BAR_Q_FREE);
+      mbar_init(&c.bars[i], is_sched_free ? (uint32_t)Cfg::SOFTMAX_WARPS + 1u
+                                          : (is_p_full || is_q_copy) ? (uint32_t)Cfg::SOFTMAX_WARPS : 1u);
     }
     *c.abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == PRODUCER_WARP && lane == 0) {
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
@@ -116,20 +137,55 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   tc_fence_after();
   c.tmem_base = *tmem_slot;
 
-  if (warp < 4) {
-    // ------------------------------ softmax warpgroup ------------------------------
+  if (warp < PRODUCER_WARP) {
+    // ------------------------------ softmax warps ------------------------------
     const int warp_q = warp & 3;
     const uint32_t lane_addr = c.tmem_base + ((uint32_t)(warp_q * 32) << 16);
     const uint32_t o_addr = lane_addr + Cfg::O_BASE;
     uint64_t* o_full = &c.bars[Cfg::BAR_O_FULL];
     const float cmul = SOFTCAP ? p.cap_out : p.scale_log2;
-    int g = 0;   // blocks processed by this CTA so far (S / P buffer = g % 2, barrier phases follow g)
+    int g = 0;   // blocks processed by this CTA so far (S / P buffer = g % SB, barrier phases follow g)
+    // Q in TMEM: thread r moves row r of tile k2's Q from the (swizzled) shared-memory tile into TMEM lane r.  Every S MMA of the previous tile has completed by then (its last S tile was
+    // awaited before that tile's last softmax step), so the columns are free.
+    [[maybe_unused]] auto stage_q = [&](int k2) -> bool {
+      if (!mbar_wait(&c.bars[Cfg::BAR_Q_FULL], k2 & 1, c.abort_flag, WAIT_Q_FULL)) return false;
+      constexpr int NCH = D / 8;   // 16-byte pieces of the row
+      const int r = warp_q * 32 + lane;
+      const uint8_t* qrow = c.sQ + r * 128;
+#pragma unroll
+      for (int cc = 0; cc < NCH; cc += 8) {
+        uint32_t w[32];
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          const int piece = cc + v, ks = piece >> 3, ci = piece & 7;
+          const uint4 x = *reinterpret_cast<const uint4*>(qrow + ks * (BM * 128) + ((ci ^ (r & 7)) << 4));
+          w[4 * v] = x.x;
+          w[4 * v + 1] = x.y;
+          w[4 * v + 2] = x.z;
+          w[4 * v + 3] = x.w;
+        }
+        tmem_st32(lane_addr + Cfg::Q_COL + cc * 4, w);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&c.bars[Cfg::BAR_QT_FULL]);
+        mbar_arrive(&c.bars[Cfg::BAR_Q_FREE]);
+      }
+      return true;
+    };
+    bool q_staged = false;   // the coming tile's Q was moved before the previous tile's epilogue
     for (int k = 0;; ++k) {
       if (!mbar_wait(&c.bars[Cfg::BAR_SCHED + (k & 1)], (k >> 1) & 1, c.abort_flag, WAIT_SCHED)) break;
       const int item = sched[k & 1];
       __syncwarp();
       if (lane == 0) mbar_arrive(&c.bars[Cfg::BAR_SCHED_FREE + (k & 1)]);   // slot may be rewritten for tile k + 2
       if (item < 0) break;
+      if constexpr (QT) {
+        if (!q_staged && !stage_q(k)) break;
+        q_staged = false;
+      }
       const TileInfo t = decode_item(item, p, sp, BN);
       const int row = t.q0 + warp_q * 32 + lane;
       float m = -1.0e30f, l = 0.f;
@@ -139,24 +195,34 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       const int lo_last = (p.causal && p.window > 0) ? (t.q0 + 127 + p.delta - p.window + 1) : -(1 << 28);
       bool ok = true;
       for (int j = t.lo; j < t.hi && ok; ++j, ++g) {
-        const int n = j - t.lo, buf = g & 1;
+        const int n = j - t.lo, buf = g % SB;
         const uint32_t s_addr = lane_addr + buf * BN;
         uint64_t* p_full = &c.bars[Cfg::BAR_P_FULL + buf];
-        ok = mbar_wait(&c.bars[Cfg::BAR_S_FULL + buf], (g >> 1) & 1, c.abort_flag, WAIT_S_FULL);
+        ok = mbar_wait(&c.bars[Cfg::BAR_S_FULL + buf], (g / SB) & 1, c.abort_flag, WAIT_S_FULL);
         if (!ok) break;
         tc_fence_after();
         const bool need_mask = (hi_first - j * BN < BN - 1) || (lo_last - j * BN > 0);
-        if (need_mask)
+        if (need_mask) {
           ok = fwd_softmax_block<Cfg, BF16, SOFTCAP, true>(c, p, s_addr, o_addr, o_full, p_full, n, g, lo_key - j * BN,
                                                            hi_key - j * BN, cmul, m, l, nullptr, 0, nullptr);
-        else
+        } else {
           ok = fwd_softmax_block<Cfg, BF16, SOFTCAP, false>(c, p, s_addr, o_addr, o_full, p_full, n, g, 0, 0, cmul, m, l,
                                                             nullptr, 0, nullptr);
+        }
       }
       if (!ok) break;
       // epilogue of this tile; the MMA issuer is already computing the next tile's first S tiles meanwhile.
       // The next tile's first P V (which overwrites O) is issued only after this warpgroup has delivered that
       // tile's first P, i.e. after the loads below have completed.
+      if constexpr (QT) {
+        // Next tile's Q first if it has landed (its first S MMAs then run under this tile's epilogue); otherwise
+        // the epilogue goes first and the move happens at the top of the loop.
+        if (mbar_test_wait(&c.bars[Cfg::BAR_SCHED + ((k + 1) & 1)], ((k + 1) >> 1) & 1) && sched[(k + 1) & 1] >= 0 &&
+            mbar_test_wait(&c.bars[Cfg::BAR_Q_FULL], (k + 1) & 1)) {
+          if (!stage_q(k + 1)) break;
+          q_staged = true;
+        }
+      }
       const int last = g - 1;
       if (!mbar_wait(o_full + (last & 1), (last >> 1) & 1, c.abort_flag, WAIT_O_FULL)) break;
       tc_fence_after();
@@ -191,7 +257,7 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       if (p.lse != nullptr && in_range) p.lse[((int64_t)t.b * p.heads + t.h) * p.lse_stride + row] = m + log2f(l);
       blocks_done = g;
     }
-  } else if (warp == 4) {
+  } else if (warp == PRODUCER_WARP) {
     // --------------------------- TMA producer + tile scheduler ---------------------------
     if (lane == 0) {
       int ring_i = 0;   // K/V ring items issued so far (continuous across tiles)
@@ -270,22 +336,31 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     const uint32_t o_tmem = c.tmem_base + Cfg::O_BASE;
     auto issue_s = [&](int slot, int gb, bool last_of_tile) {
       const uint32_t b0 = k_lo + (uint32_t)(slot * (Cfg::KV_STAGE_BYTES >> 4));
-      const uint32_t s_tmem = c.tmem_base + (gb & 1) * BN;
+      const uint32_t s_tmem = c.tmem_base + (gb % SB) * BN;
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
         const uint32_t a_off = (uint32_t)(((kk / 4) * (BM * 128) + (kk % 4) * 32) >> 4);
         const uint32_t b_off = (uint32_t)(((kk / 4) * (BN * 128) + (kk % 4) * 32) >> 4);
-        if (kk == 0)
-          umma_ss_c<IDESC_S, 0>(s_tmem, q_lo + a_off, b0 + b_off, desc_hi);
-        else
-          umma_ss_c<IDESC_S, 1>(s_tmem, q_lo + a_off, b0 + b_off, desc_hi);
+        if constexpr (QT) {
+          // 16 dims (one K step) = 8 TMEM columns of packed 16-bit pairs
+          const uint32_t a_tmem = c.tmem_base + Cfg::Q_COL + kk * 8;
+          if (kk == 0)
+            umma_ts_c<IDESC_S, 0>(s_tmem, a_tmem, b0 + b_off, desc_hi);
+          else
+            umma_ts_c<IDESC_S, 1>(s_tmem, a_tmem, b0 + b_off, desc_hi);
+        } else {
+          if (kk == 0)
+            umma_ss_c<IDESC_S, 0>(s_tmem, q_lo + a_off, b0 + b_off, desc_hi);
+          else
+            umma_ss_c<IDESC_S, 1>(s_tmem, q_lo + a_off, b0 + b_off, desc_hi);
+        }
       }
-      umma_commit(&c.bars[Cfg::BAR_S_FULL + (gb & 1)]);
-      if (last_of_tile) umma_commit(&c.bars[Cfg::BAR_Q_FREE]);   // no later MMA reads this tile's Q
+      umma_commit(&c.bars[Cfg::BAR_S_FULL + (gb % SB)]);
+      if (!QT && last_of_tile) umma_commit(&c.bars[Cfg::BAR_Q_FREE]);   // no later MMA reads this tile's Q
     };
     auto issue_pv = [&](int slot, int gb, bool first_of_tile) {
       const uint32_t b0 = v_lo + (uint32_t)(slot * (Cfg::KV_STAGE_BYTES >> 4));
-      const uint32_t s_tmem = c.tmem_base + (gb & 1) * BN;
+      const uint32_t s_tmem = c.tmem_base + (gb % SB) * BN;
       if (first_of_tile)
         umma_ts_c<IDESC_PV, 0>(o_tmem, s_tmem, b0, desc_hi);
       else
@@ -305,7 +380,8 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       if (item < 0) break;
       const TileInfo t = decode_item(item, p, sp, BN);
       const int nb = t.hi - t.lo;
-      ok = mbar_wait(&c.bars[Cfg::BAR_Q_FULL], k & 1, c.abort_flag, WAIT_Q_FULL);
+      ok = mbar_wait(&c.bars[QT ? Cfg::BAR_QT_FULL : Cfg::BAR_Q_FULL], k & 1, c.abort_flag, WAIT_Q_FULL);
+      if (QT) tc_fence_after();
       // S of the first SB blocks
       for (int n = 0; n < SB && n < nb && ok; ++n) {
         const int slot = ring_i % SL, ph = (ring_i / SL) & 1;
@@ -337,7 +413,7 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         const int nvslot = ring_i % SL, nvph = (ring_i / SL) & 1;
         if (has_v) ++ring_i;
         const int gb = g0 + n;
-        ok = mbar_wait(&c.bars[Cfg::BAR_P_FULL + (gb & 1)], (gb >> 1) & 1, c.abort_flag, WAIT_P_FULL);
+        ok = mbar_wait(&c.bars[Cfg::BAR_P_FULL + (gb % SB)], (gb / SB) & 1, c.abort_flag, WAIT_P_FULL);
         if (!ok) break;
         tc_fence_after();
         if (elect_one()) {
@@ -369,7 +445,7 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         const int gb = g0 + n;
         ok = mbar_wait(&c.bars[Cfg::BAR_FULL + vslot], vph, c.abort_flag, WAIT_V_FULL);
         if (ok && has_k) ok = mbar_wait(&c.bars[Cfg::BAR_FULL + kslot], kph, c.abort_flag, WAIT_K_FULL);
-        if (ok) ok = mbar_wait(&c.bars[Cfg::BAR_P_FULL + (gb & 1)], (gb >> 1) & 1, c.abort_flag, WAIT_P_FULL);
+        if (ok) ok = mbar_wait(&c.bars[Cfg::BAR_P_FULL + (gb % SB)], (gb / SB) & 1, c.abort_flag, WAIT_P_FULL);
         if (!ok) break;
         tc_fence_after();
         if (elect_one()) {
@@ -444,7 +520,7 @@ int launch_attn_fwd_persist(const CUtensorMap& tq, const CUtensorMap& tk, const 
     sp.group_heads = gh;
   }
   const int grid = std::min(sp.total_items, Cfg::CTAS_PER_SM * sm_count());
-  kern<<<grid, 192, Cfg::SMEM_BYTES_P, stream>>>(tq, tk, tv, p, sp);
+  kern<<<grid, Cfg::THREADS_P, Cfg::SMEM_BYTES_P, stream>>>(tq, tk, tv, p, sp);
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
 }

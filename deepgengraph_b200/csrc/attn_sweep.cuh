@@ -320,19 +320,18 @@ __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, con
 
   float2 acc2 = make_float2(0.f, 0.f), sq2 = make_float2(0.f, 0.f);
   // One 32-column chunk of the tile: p = exp2(x - L_i) for the thread's key against 32 queries.
-  auto chunk_body = [&](auto mask_tag, const uint32_t (&sr)[32], int ch, const float* lse_s, const float* noise_col,
-                        int lo_c, int hi_c, float qbase, int i0) {
+  // cap_tag (soft-cap only): no lane of the warp holds |raw / cap| > 1 in this chunk -> polynomial branch alone
+  auto chunk_body = [&](auto mask_tag, auto cap_tag, const uint32_t (&sr)[32], int ch, const float* lse_s,
+                        const float* noise_col, int lo_c, int hi_c, float qbase, int i0) {
     constexpr bool MASK = decltype(mask_tag)::value;
+    [[maybe_unused]] constexpr bool cap_poly_only = decltype(cap_tag)::value;
     const float2 c2 = make_float2(cmul, cmul);
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
       const float4 L = *reinterpret_cast<const float4*>(lse_s + ch * 32 + i);
       float sv[4] = {__uint_as_float(sr[i]), __uint_as_float(sr[i + 1]), __uint_as_float(sr[i + 2]),
                      __uint_as_float(sr[i + 3])};
-      if constexpr (SOFTCAP) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u) sv[u] = tanh_approx(sv[u] * p.cap_in) * p.cap_out;
-      }
+      if constexpr (SOFTCAP) softcap4(sv, p.cap_in, p.cap_out, cap_poly_only);
       float2 e0, e1;
       if constexpr (KF) {
         const float2 it2 = make_float2(p.inv_tau, p.inv_tau);
@@ -423,10 +422,20 @@ __device__ __forceinline__ void sweep_compute_colsum(const SweepCtx<Cfg>& c, con
       const int ch = ch0 + cc;
       tmem_ld_wait();
       if (cc + 1 < NCH) tmem_ld32(lane_addr + tb * BX + (ch + 1) * 32, sr[(cc + 1) & 1]);
-      if (need_mask)
-        chunk_body(std::true_type{}, sr[cc & 1], ch, lse_s, noise_col, lo_c, hi_c, (float)(i0 + 1), i0);
-      else
-        chunk_body(std::false_type{}, sr[cc & 1], ch, lse_s, noise_col, lo_c, hi_c, (float)(i0 + 1), i0);
+      auto run_chunk = [&](auto cap_tag) {
+        if (need_mask)
+          chunk_body(std::true_type{}, cap_tag, sr[cc & 1], ch, lse_s, noise_col, lo_c, hi_c, (float)(i0 + 1), i0);
+        else
+          chunk_body(std::false_type{}, cap_tag, sr[cc & 1], ch, lse_s, noise_col, lo_c, hi_c, (float)(i0 + 1), i0);
+      };
+      if constexpr (SOFTCAP) {
+        if (softcap_chunk_poly_only(sr[cc & 1], p.cap_in))
+          run_chunk(std::true_type{});
+        else
+          run_chunk(std::false_type{});
+      } else {
+        run_chunk(std::false_type{});
+      }
       if (tl_on && cc < 4) B200_TL(tl_base + 3 + cc);
     }
     // this TMEM buffer and this auxiliary stage may be refilled
@@ -502,15 +511,13 @@ __device__ __forceinline__ void sweep_compute_colsum_grouped(const SweepCtx<Cfg>
       uint32_t sr[32];
       tmem_ld32(lane_addr + tb * BX + ch * 32, sr);
       tmem_ld_wait();
+      [[maybe_unused]] const bool cap_poly_only = SOFTCAP && softcap_chunk_poly_only(sr, p.cap_in);
 #pragma unroll
       for (int i = 0; i < 32; i += 4) {
         const float4 L = *reinterpret_cast<const float4*>(lse_s + ch * 32 + i);
         float sv[4] = {__uint_as_float(sr[i]), __uint_as_float(sr[i + 1]), __uint_as_float(sr[i + 2]),
                        __uint_as_float(sr[i + 3])};
-        if constexpr (SOFTCAP) {
-#pragma unroll
-          for (int u = 0; u < 4; ++u) sv[u] = tanh_approx(sv[u] * p.cap_in) * p.cap_out;
-        }
+        if constexpr (SOFTCAP) softcap4(sv, p.cap_in, p.cap_out, cap_poly_only);
         const float2 c2 = make_float2(cmul, cmul);
         const float2 e0 = ffma2(make_float2(sv[0], sv[1]), c2, make_float2(-L.x, -L.y));
         const float2 e1 = ffma2(make_float2(sv[2], sv[3]), c2, make_float2(-L.z, -L.w));

@@ -12,6 +12,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <mutex>
+#include <type_traits>
 
 #include "../../include/b200attn.h"
 
@@ -438,6 +439,59 @@ __device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
       : "l"(reinterpret_cast<uint64_t&>(a)), "l"(reinterpret_cast<uint64_t&>(b)));
   return d;
 }
+// Soft-cap tanh (kernels/gemma2.py:30-34 caps the logits with cap * tanh(s / cap)), y = s / cap:
+//   |y| <= 1 -- every logit up to the cap itself -- : y * r(y^2), r an own degree-4 minimax fit of tanh(y) / y
+//              (max relative error 7e-6, seventy times tighter than tanh.approx), on the FMA pipe;
+//   |y| >  1 : tanh.approx.
+// The choice depends on the element's own value only, so the forward kernel and the score sweeps, which visit the
+// elements in different groupings, evaluate the same function on the same element; callers vote per block whether
+// any lane holds an element of the second kind and otherwise never issue the special-function instruction (the
+// exponentials already load that unit: a tanh.approx per element doubled its work).
+constexpr float kCapPolyMax = 1.0f;
+constexpr float kCapR0 = 0.999993085861206f, kCapR1 = -0.332980751991272f, kCapR2 = 0.1303686499595642f,
+                kCapR3 = -0.04481850564479828f, kCapR4 = 0.009036950767040253f;
+// r(y^2) * mul for two elements (mul folds the factor that follows the tanh into the polynomial)
+__device__ __forceinline__ float2 softcap_r2(float2 y, float mul) {
+  const float2 q = fmul2(y, y);
+  float2 r = ffma2(q, make_float2(kCapR4 * mul, kCapR4 * mul), make_float2(kCapR3 * mul, kCapR3 * mul));
+  r = ffma2(r, q, make_float2(kCapR2 * mul, kCapR2 * mul));
+  r = ffma2(r, q, make_float2(kCapR1 * mul, kCapR1 * mul));
+  r = ffma2(r, q, make_float2(kCapR0 * mul, kCapR0 * mul));
+  return r;
+}
+// the full function for one element (both branches evaluated, selected by |y|)
+__device__ __forceinline__ float softcap_tanh(float y) {
+  const float q = y * y;
+  float r = fmaf(q, kCapR4, kCapR3);
+  r = fmaf(r, q, kCapR2);
+  r = fmaf(r, q, kCapR1);
+  r = fmaf(r, q, kCapR0);
+  return fabsf(y) <= kCapPolyMax ? y * r : tanh_approx(y);
+}
+
+// warp vote over a 32-column chunk of raw logits: true when every lane's |raw * cap_in| stays <= 1
+__device__ __forceinline__ bool softcap_chunk_poly_only(const uint32_t (&sr)[32], float cap_in) {
+  float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    a0 = fmax3(a0, fabsf(__uint_as_float(sr[i])), fabsf(__uint_as_float(sr[i + 1])));
+    a1 = fmax3(a1, fabsf(__uint_as_float(sr[i + 2])), fabsf(__uint_as_float(sr[i + 3])));
+  }
+  return !__any_sync(0xffffffffu, fmaxf(a0, a1) * cap_in > kCapPolyMax);
+}
+// sv <- cap_out * softcap_tanh(sv * cap_in) for four raw logits (poly_only is warp-uniform)
+__device__ __forceinline__ void softcap4(float (&sv)[4], float cap_in, float cap_out, bool poly_only) {
+  if (poly_only) {
+    const float2 a2 = make_float2(cap_in, cap_in);
+    const float2 y0 = fmul2(make_float2(sv[0], sv[1]), a2), y1 = fmul2(make_float2(sv[2], sv[3]), a2);
+    const float2 t0 = fmul2(y0, softcap_r2(y0, cap_out)), t1 = fmul2(y1, softcap_r2(y1, cap_out));
+    sv[0] = t0.x, sv[1] = t0.y, sv[2] = t1.x, sv[3] = t1.y;
+  } else {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) sv[u] = softcap_tanh(sv[u] * cap_in) * cap_out;
+  }
+}
+
 // warp-group register re-allocation (all 128 threads of an aligned group of four warps execute it)
 template <int N>
 __device__ __forceinline__ void reg_alloc() {
