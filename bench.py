@@ -260,6 +260,41 @@ def time_op(fns, iters, warmup):
   return ts[len(ts) // 2], ts[0]
 
 
+def time_graph(fns, iters):
+  """The batches of `time_op` captured once into a CUDA graph and replayed: per-launch GPU time without the host's
+  cost of issuing the launch (a Python call into the library costs 15-20 us, as much as the shortest kernels here
+  run).  Returns (median, min) in microseconds, or None when the operation cannot be captured."""
+  if callable(fns):
+    fns = [fns]
+  per_batch = max(len(fns), 4)
+  side = torch.cuda.Stream()
+  try:
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+      for i in range(max(3, len(fns))):
+        fns[i % len(fns)]()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+      for k in range(per_batch):
+        fns[k % len(fns)]()
+  except Exception:  # noqa: BLE001 -- the eager figure stands alone
+    torch.cuda.synchronize()
+    return None
+  for _ in range(3):
+    graph.replay()
+  batches = max(10, -(-iters // per_batch))
+  pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(batches)]
+  for e0, e1 in pairs:
+    e0.record()
+    graph.replay()
+    e1.record()
+  torch.cuda.synchronize()
+  ts = sorted(e0.elapsed_time(e1) * 1e3 / per_batch for e0, e1 in pairs)
+  return ts[len(ts) // 2], ts[0]
+
+
 def buffer_sets(footprint_bytes, cap=12):
   """How many independent buffer sets of `footprint_bytes` make a rotation that outgrows L2 (4 x L2, at most `cap`)."""
   return int(max(1, min(cap, -(-4 * L2_BYTES // max(1, footprint_bytes)))))
@@ -277,8 +312,10 @@ def sub_records(dev, peaks, iters, warmup):
   def randn(*shape, dtype=torch.bfloat16, scale=1.0):
     return (torch.randn(*shape, generator=gen, device=dev, dtype=torch.float32) * scale).to(dtype)
 
-  def record(name, workload, fns, bound, work, extra=None):
-    """work = algorithmic flops (tensor) or bytes (hbm) per launch."""
+  def record(name, workload, fns, bound, work, extra=None, graph=False):
+    """work = algorithmic flops (tensor) or bytes (hbm) per launch.  graph=True (kernels of a few tens of
+    microseconds): the same batches are also replayed from a CUDA graph; `us_graph_*` and `*_graph` are then the GPU's
+    own time per launch, `us_median` stays the eager call through the Python API."""
     n_sets = len(fns) if isinstance(fns, list) else 1
     med, mn = time_op(fns, iters, warmup)
     r = {"name": name, "workload": workload, "us_median": med, "us_min": mn, "bound": bound, "buffer_sets": n_sets}
@@ -286,6 +323,16 @@ def sub_records(dev, peaks, iters, warmup):
       r.update(tflops=work / med / 1e6, frac_of_measured_peak=work / med / 1e6 / peak_tf)
     else:
       r.update(gbs=work / med / 1e3, algorithmic_bytes=work, frac_of_measured_peak=work / med / 1e3 / peak_bw)
+    if graph:
+      tg = time_graph(fns, iters)
+      if tg is None:
+        r["graph"] = "not capturable"
+      else:
+        r.update(us_graph_median=tg[0], us_graph_min=tg[1])
+        if bound == "tensor":
+          r.update(tflops_graph=work / tg[0] / 1e6, frac_of_measured_peak_graph=work / tg[0] / 1e6 / peak_tf)
+        else:
+          r.update(gbs_graph=work / tg[0] / 1e3, frac_of_measured_peak_graph=work / tg[0] / 1e3 / peak_bw)
     if extra:
       r.update(extra)
     recs.append(r)
@@ -314,7 +361,7 @@ def sub_records(dev, peaks, iters, warmup):
   scores = [att.attn_score_fwd(*t)[1] for t in sets]
   record("config3_kv_evict_topk", w3 + ", budget 512: topk -> sort -> gather",
          [(lambda t=t, sc=sc: att.kv_evict_topk(sc, t[1], t[2], 512)) for t, sc in zip(sets, scores)], "hbm",
-         scores[0].numel() * 4 + 4 * b3 * 512 * h3 * D * 2)
+         scores[0].numel() * 4 + 4 * b3 * 512 * h3 * D * 2, graph=True)
   del sets, scores
 
   # the reference's default shape (run_kernel.py:20-24; the workload of its Fig. 14): batch 1, 32 heads, seq 4096, fp16
@@ -331,7 +378,7 @@ def sub_records(dev, peaks, iters, warmup):
   for s in (1024, 2048, 4096, 8192):
     sets = qkv_sets(1, s, 32, 32, D)
     record(f"sweep_attn_s{s}", f"B1 H32 S{s} D128 bf16 causal", over(sets, lambda q, k, v: att.attn_fwd(q, k, v)),
-           "tensor", causal_flops(1, 32, s, D))
+           "tensor", causal_flops(1, 32, s, D), graph=s <= 2048)
     record(f"sweep_h2o_s{s}", f"B1 H32 S{s} D128 bf16 causal, out + sum_i p",
            over(sets, lambda q, k, v: att.attn_score_fwd(q, k, v)), "tensor", causal_flops(1, 32, s, D))
     del sets
@@ -374,9 +421,9 @@ def sub_records(dev, peaks, iters, warmup):
   n = buffer_sets(2 * T * hid * sz)
   xs = [(randn(T, hid), torch.empty(T, hid, dtype=torch.bfloat16, device=dev)) for _ in range(n)]
   record("rms_norm", f"[{T}, {hid}] bf16", [(lambda t=t: ops.rms_norm(t[1], t[0], wn, cfg.eps)) for t in xs], "hbm",
-         2 * T * hid * sz + hid * sz)
+         2 * T * hid * sz + hid * sz, graph=True)
   record("fused_add_rms_norm", f"[{T}, {hid}] bf16, in place",
-         [(lambda t=t: ops.fused_add_rms_norm(t[0], t[1], wn, cfg.eps)) for t in xs], "hbm", 4 * T * hid * sz)
+         [(lambda t=t: ops.fused_add_rms_norm(t[0], t[1], wn, cfg.eps)) for t in xs], "hbm", 4 * T * hid * sz, graph=True)
   del xs
   n = buffer_sets(3 * T * cfg.intermediate * sz, cap=4)
   gs = [(randn(T, 2 * cfg.intermediate), torch.empty(T, cfg.intermediate, dtype=torch.bfloat16, device=dev)) for _ in range(n)]
@@ -390,7 +437,7 @@ def sub_records(dev, peaks, iters, warmup):
   rs = [(randn(T, cfg.heads * cfg.head_dim), randn(T, cfg.kv_heads * cfg.head_dim)) for _ in range(n)]
   record("rotary_embedding_online", f"q [{T}, {cfg.heads}x{cfg.head_dim}], k [{T}, {cfg.kv_heads}x{cfg.head_dim}] bf16",
          [(lambda t=t: ops.rotary_embedding_online(pos, t[0], t[1], cfg.head_dim, cfg.rope_theta)) for t in rs], "hbm",
-         2 * T * (cfg.heads + cfg.kv_heads) * cfg.head_dim * sz + 4 * T)
+         2 * T * (cfg.heads + cfg.kv_heads) * cfg.head_dim * sz + 4 * T, graph=True)
   del rs
 
   # ---- the reference's Llama-shaped layer with a score variant and the eviction fused in (models/h2o.py:34-86),

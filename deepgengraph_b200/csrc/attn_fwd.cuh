@@ -615,10 +615,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   // A launch that follows an expired wait on this device drains immediately (the status word stays
   // set until the host reads it), so that one stuck kernel cannot stall a whole queue of launches.
+  // (the word is loaded here and looked at after the set-up, whose barrier it shares)
   __shared__ int s_skip;
-  if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(&g_device_status);
-  __syncthreads();
-  if (s_skip != 0) return;
+  int status_now = 0;
+  if (threadIdx.x == 0) status_now = *reinterpret_cast<volatile int*>(&g_device_status);
   [[maybe_unused]] const uint64_t cta_start_ns = global_timer_ns();
   [[maybe_unused]] const long long cta_start_clk = clock64();
   B200_TL_INIT();
@@ -669,10 +669,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
     tmem_relinquish();
   }
+  if (threadIdx.x == 0) s_skip = status_now;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   c.tmem_base = *tmem_slot;
+  if (s_skip != 0) {
+    if (warp == 0) tmem_dealloc(c.tmem_base, Cfg::TMEM_COLS);
+    return;
+  }
   if (threadIdx.x == 0) B200_TL((3 * 64 + 62) * 8 + 1);   // set-up done (barriers, TMEM)
 
   if (warp < NQ * 4) {

@@ -93,10 +93,12 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
+  // A launch that follows an expired wait on this device drains immediately (the status word stays set until the
+  // host reads it).  The word is loaded here and looked at after the set-up below, whose barrier it shares: a
+  // global load of its own before anything else costs every launch most of a microsecond.
   __shared__ int s_skip;
-  if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(&g_device_status);
-  __syncthreads();
-  if (s_skip != 0) return;   // (the tile counter is untouched: the host zeroes it when it clears the status word)
+  int status_now = 0;
+  if (threadIdx.x == 0) status_now = *reinterpret_cast<volatile int*>(&g_device_status);
 
   [[maybe_unused]] const uint64_t cta_start_ns = global_timer_ns();
   [[maybe_unused]] const long long cta_start_clk = clock64();
@@ -132,10 +134,15 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
     tmem_relinquish();
   }
+  if (threadIdx.x == 0) s_skip = status_now;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   c.tmem_base = *tmem_slot;
+  if (s_skip != 0) {   // (the tile counter is untouched: the host zeroes it when it clears the status word)
+    if (warp == 0) tmem_dealloc(c.tmem_base, Cfg::TMEM_COLS);
+    return;
+  }
 
   if (warp < PRODUCER_WARP) {
     // ------------------------------ softmax warps ------------------------------
@@ -263,7 +270,8 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       int ring_i = 0;   // K/V ring items issued so far (continuous across tiles)
       bool ok = true;
       for (int k = 0; ok; ++k) {
-        const int item = (int)atomicAdd(&sp.counter[0], 1u);
+        // the first tile of a CTA is its own index (no round trip to the counter before the first load is issued)
+        const int item = k == 0 ? (int)blockIdx.x : (int)(gridDim.x + atomicAdd(&sp.counter[0], 1u));
         const bool valid = item < sp.total_items;
         // Slot k % 2 still holds the descriptor of tile k-2 until the four softmax warps and the issuer have all
         // read it (with tiles of one or two key blocks the issuer can finish a tile's S MMAs, and this thread

@@ -662,11 +662,11 @@ attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   // A launch that follows an expired wait on this device drains immediately (the status word stays
-  // set until the host reads it), so that one stuck kernel cannot stall a whole queue of launches.
+  // set until the host reads it), so that one stuck kernel cannot stall a whole queue of launches.  The word is
+  // loaded here and looked at after the set-up below, whose barrier it shares.
   __shared__ int s_skip;
-  if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(&g_device_status);
-  __syncthreads();
-  if (s_skip != 0) return;
+  int status_now = 0;
+  if (threadIdx.x == 0) status_now = *reinterpret_cast<volatile int*>(&g_device_status);
 
   B200_TL_INIT();
   SweepCtx<Cfg> c;
@@ -733,10 +733,15 @@ attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
     tmem_relinquish();
   }
+  if (threadIdx.x == 0) s_skip = status_now;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   c.tmem_base = *tmem_slot;
+  if (s_skip != 0) {
+    if (warp == 0) tmem_dealloc(c.tmem_base, Cfg::TMEM_COLS);
+    return;
+  }
 
   if (warp < CW) {
     if constexpr (Cfg::A_TMEM) if (warp < 4) {
