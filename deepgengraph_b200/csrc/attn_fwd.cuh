@@ -335,8 +335,9 @@ __device__ __forceinline__ bool fwd_softmax_block(const FwdCtx<Cfg, BF16>& c, co
                                                   bool* next_ready = nullptr) {
   constexpr int D = Cfg::D, BN = Cfg::BN;
   const int lane = threadIdx.x & 31;
-  [[maybe_unused]] const int tl_base = (((int)(threadIdx.x >> 7)) * 64 + (n & 63)) * 8;
-  [[maybe_unused]] const bool tl_on = (threadIdx.x & 127) == 0;
+  // (tuning builds stamp the first 64 blocks a CTA walks)
+  [[maybe_unused]] const int tl_base = (((int)(threadIdx.x >> 7)) * 64 + (g & 63)) * 8;
+  [[maybe_unused]] const bool tl_on = (threadIdx.x & 127) == 0 && g < 64;
   if (tl_on) B200_TL(tl_base + 0);
   uint32_t sr[BN / 32][32];
 #pragma unroll
@@ -354,6 +355,7 @@ __device__ __forceinline__ bool fwd_softmax_block(const FwdCtx<Cfg, BF16>& c, co
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
       float v[4];
+      [[maybe_unused]] float va[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         float s = __uint_as_float(sr[ch][i + u]);
@@ -368,12 +370,14 @@ __device__ __forceinline__ bool fwd_softmax_block(const FwdCtx<Cfg, BF16>& c, co
           if constexpr (!SOFTCAP) sr[ch][i + u] = __float_as_uint(s);
         }
         v[u] = s;
-        if constexpr (SOFTCAP) {
-          if (u < 2) ab0 = fmaxf(ab0, sa); else ab1 = fmaxf(ab1, sa);
-        }
+        if constexpr (SOFTCAP) va[u] = sa;
       }
       mx0 = fmax3(mx0, v[0], v[1]);
       mx1 = fmax3(mx1, v[2], v[3]);
+      if constexpr (SOFTCAP) {
+        ab0 = fmax3(ab0, va[0], va[1]);
+        ab1 = fmax3(ab1, va[2], va[3]);
+      }
     }
   }
   float m_blk = fmaxf(mx0, mx1);   // -inf when the whole row is masked inside this block
@@ -730,7 +734,7 @@ int launch_attn_fwd_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUte
   return B200_OK;
 }
 
-// persistent variant for head_dim 128 (attn_fwd_persist.cuh)
+// persistent variant (attn_fwd_persist.cuh)
 template <int D_, bool BF16, bool SOFTCAP>
 int launch_attn_fwd_persist(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
                             cudaStream_t stream);

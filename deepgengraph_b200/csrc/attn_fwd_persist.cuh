@@ -103,6 +103,7 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   [[maybe_unused]] const uint64_t cta_start_ns = global_timer_ns();
   [[maybe_unused]] const long long cta_start_clk = clock64();
   [[maybe_unused]] int blocks_done = 0;
+  B200_TL_INIT();
   FwdCtx<Cfg, BF16> c;
   c.sQ = smem;
   c.sKV = c.sQ + Cfg::Q_TILE_BYTES;
@@ -205,8 +206,10 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         const int n = j - t.lo, buf = g % SB;
         const uint32_t s_addr = lane_addr + buf * BN;
         uint64_t* p_full = &c.bars[Cfg::BAR_P_FULL + buf];
+        if (threadIdx.x == 0 && g < 64) B200_TL((g & 63) * 8 + 5);
         ok = mbar_wait(&c.bars[Cfg::BAR_S_FULL + buf], (g / SB) & 1, c.abort_flag, WAIT_S_FULL);
         if (!ok) break;
+        if (threadIdx.x == 0 && g < 64) B200_TL((g & 63) * 8 + 6);
         tc_fence_after();
         const bool need_mask = (hi_first - j * BN < BN - 1) || (lo_last - j * BN > 0);
         if (need_mask) {
@@ -421,12 +424,15 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         const int nvslot = ring_i % SL, nvph = (ring_i / SL) & 1;
         if (has_v) ++ring_i;
         const int gb = g0 + n;
+        if (lane == 0 && gb < 64) B200_TL((3 * 64 + (gb & 63)) * 8 + 0);
         ok = mbar_wait(&c.bars[Cfg::BAR_P_FULL + (gb % SB)], (gb / SB) & 1, c.abort_flag, WAIT_P_FULL);
         if (!ok) break;
         tc_fence_after();
         if (elect_one()) {
+          if (gb < 64) B200_TL((3 * 64 + (gb & 63)) * 8 + 1);
           issue_pv(vslot, gb, n == 0);
           umma_commit(&c.bars[Cfg::BAR_EMPTY + vslot]);
+          if (gb < 64) B200_TL((2 * 64 + (gb & 63)) * 8 + 1);
         }
         __syncwarp();
         if (has_k) ok = mbar_wait(&c.bars[Cfg::BAR_FULL + kslot], kph, c.abort_flag, WAIT_K_FULL);
@@ -435,8 +441,10 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         tc_fence_after();
         if (has_k) {
           if (elect_one()) {
+            if (gb < 64) B200_TL((2 * 64 + (gb & 63)) * 8 + 2);
             issue_s(kslot, gb + SB, n + SB == nb - 1);
             umma_commit(&c.bars[Cfg::BAR_EMPTY + kslot]);
+            if (gb < 64) B200_TL((2 * 64 + (gb & 63)) * 8 + 3);
           }
           __syncwarp();
         }
@@ -476,6 +484,7 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(c.tmem_base, Cfg::TMEM_COLS);
+  B200_TL_FLUSH();
   B200_TL_CTA(cta_start_ns, cta_start_clk, blocks_done);
 }
 
