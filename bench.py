@@ -20,7 +20,9 @@ Further records on the same line:
                    (attention, whole layer), the reference's Llama-shaped H2O layer, the five bandwidth ops, the
                    reference's default shape (batch 1, 32 heads, seq 4096, fp16) and the seq-length sweep:
                    median and min per launch over batches of launches (CUDA events around a batch) that rotate over
-                   buffer sets whose total footprint is several times L2
+                   buffer sets whose total footprint is several times L2; every record starts from a GPU left idle for
+                   0.3 s (as the headline's timed region does); kernels of a few tens of microseconds are also
+                   replayed from a CUDA graph (`us_graph_*`: GPU time without the host's launch cost)
 
 --impl reference times the CPU port alone (all host threads) and prints the same line shape.
 FLOPs follow the reference's own formula 4*B*H*S*S*D/2 (run_kernel.py:24).
@@ -235,6 +237,9 @@ def run_reference_arm(args, rank, world):
 L2_BYTES = 126 << 20
 
 
+SUB_IDLE_S = 0.3   # idle time before each sub-record's warm-up
+
+
 def time_op(fns, iters, warmup):
   """Median and minimum time per launch (microseconds).  `fns` are closures of the SAME operation on different buffer
   sets whose total footprint exceeds L2 several times over (or a single closure whose own inputs do): a timed batch
@@ -317,6 +322,10 @@ def sub_records(dev, peaks, iters, warmup):
     microseconds): the same batches are also replayed from a CUDA graph; `us_graph_*` and `*_graph` are then the GPU's
     own time per launch, `us_median` stays the eager call through the Python API."""
     n_sets = len(fns) if isinstance(fns, list) else 1
+    # Every record starts from an idle GPU, as the headline's timed region does: looping for seconds these kernels
+    # run into the board's power cap and the SM clock settles 10-25 % lower (the sustained figures are in DESIGN.md).
+    torch.cuda.synchronize()
+    time.sleep(SUB_IDLE_S)
     med, mn = time_op(fns, iters, warmup)
     r = {"name": name, "workload": workload, "us_median": med, "us_min": mn, "bound": bound, "buffer_sets": n_sets}
     if bound == "tensor":
@@ -324,6 +333,8 @@ def sub_records(dev, peaks, iters, warmup):
     else:
       r.update(gbs=work / med / 1e3, algorithmic_bytes=work, frac_of_measured_peak=work / med / 1e3 / peak_bw)
     if graph:
+      torch.cuda.synchronize()
+      time.sleep(SUB_IDLE_S)
       tg = time_graph(fns, iters)
       if tg is None:
         r["graph"] = "not capturable"
@@ -667,6 +678,7 @@ def main():
     torch.cuda.empty_cache()
     if world == 1 and not args.no_sub:
       line["sub"] = sub_records(dev, peaks, args.sub_iters, 8)
+      line["config"]["sub_idle_s"] = SUB_IDLE_S
     if world == 1 and not args.no_cpu_baseline:
       tf, cores, sample = cpu_reference_sample(budget_s=15.0)
       line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample}
