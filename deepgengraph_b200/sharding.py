@@ -9,6 +9,9 @@ The only communication is optional and off the critical path: gathering the smal
 needs them where the layer's cache lives).  That gather is one NCCL all-gather over NVLink/NVSwitch;
 attention outputs stay sharded.
 
+The plain attention can also be cut along its query rows (row_ranges / run_row_sharded below) when a problem has
+fewer units than GPUs.
+
 The reference is single-GPU (our_env.sh:35,52); this module has no counterpart there.
 """
 from dataclasses import dataclass
@@ -76,6 +79,88 @@ def run_sharded(fn, q, k, v, world: int, rank: int, extra=None, dense: bool = Tr
   for piece in shard_pieces(q.size(0), k.size(2), world, rank):
     args = slice_piece(q, k, v, piece, group, extra, dense)
     out.append((piece, fn(*args)))
+  return out
+
+
+# --------------------------------------------------------------------------------------------
+# Query-row sharding of the PLAIN attention, for problems with fewer (batch, kv-head) units than GPUs (config 5 has
+# eight).  Attention rows are independent, so a rank may also own a range of query rows of a unit: it needs the keys
+# up to its last row only, and no reduction follows.  (The score variants sum over queries; cutting their rows would
+# need one -- they shard by units only.)
+# --------------------------------------------------------------------------------------------
+def row_ranges(q_len: int, kv_len: int, parts: int, causal: bool = True, window: int = 0,
+               align: int = 128) -> List[Tuple[int, int]]:
+  """Cuts the query rows [0, q_len) into `parts` contiguous ranges of about equal WORK -- visible (query, key) pairs
+  under the causal / sliding-window mask -- with boundaries on multiples of `align` rows: query tiles stay whole, so
+  a range computes exactly what the full problem computes for those rows.  Fewer than `parts` ranges come back when
+  there are fewer tiles; no range is empty."""
+  if parts <= 0 or q_len <= 0 or kv_len < q_len:
+    raise ValueError(f"bad row split: q_len {q_len}, kv_len {kv_len}, parts {parts}")
+  delta = kv_len - q_len
+  n_tiles = -(-q_len // align)
+
+  def visible(i):
+    hi = min(i + delta, kv_len - 1) if causal else kv_len - 1
+    lo = max(0, i + delta - window + 1) if (causal and window > 0) else 0
+    return hi - lo + 1
+  tile_work = [sum(visible(i) for i in (t * align, min(q_len, (t + 1) * align) - 1)) * 0.5 *
+               (min(q_len, (t + 1) * align) - t * align) for t in range(n_tiles)]   # trapezoid: work is linear per tile
+  total = sum(tile_work)
+  parts = min(parts, n_tiles)
+  cuts, acc, nxt = [0], 0.0, 1
+  for t in range(n_tiles):
+    acc += tile_work[t]
+    tiles_left, parts_left = n_tiles - (t + 1), parts - nxt
+    if nxt < parts and (acc >= total * nxt / parts or tiles_left == parts_left):
+      cuts.append(t + 1)
+      nxt += 1
+  cuts.append(n_tiles)
+  return [(cuts[i] * align, min(q_len, cuts[i + 1] * align)) for i in range(len(cuts) - 1) if cuts[i + 1] > cuts[i]]
+
+
+def slice_rows(q, k, v, r0: int, r1: int, causal: bool = True):
+  """Views of the inputs that make attention of query rows [r0, r1) a problem of its own: the rows of q, and the keys
+  the last of them can see.  With the mask aligned bottom-right (key j visible to row i iff j <= i + kv_len - q_len,
+  kernels/attn.py:22-23) the slice's offset r1 + (kv_len - q_len) - (r1 - r0) equals the full problem's for the same
+  rows; a sliding window is relative to the row and carries over unchanged."""
+  kv_hi = k.size(1) if not causal else r1 + (k.size(1) - q.size(1))
+  return q[:, r0:r1], k[:, :kv_hi], v[:, :kv_hi]
+
+
+@dataclass(frozen=True)
+class RowPiece:
+  """Query rows [r0, r1) of kv head hk (with its query heads) of batch element b."""
+  b: int
+  hk: int
+  r0: int
+  r1: int
+
+
+def row_shard_pieces(batch: int, kv_heads: int, q_len: int, kv_len: int, world: int, rank: int, causal: bool = True,
+                     window: int = 0) -> List[RowPiece]:
+  """This rank's pieces when every unit is cut into world // units row ranges (at least one): the (unit, range) pairs
+  are numbered unit-major and dealt out in contiguous, balanced runs like the units themselves."""
+  units = batch * kv_heads
+  ranges = row_ranges(q_len, kv_len, max(1, world // units), causal, window)
+  lo, hi = unit_range(units * len(ranges), world, rank)
+  pieces = []
+  for idx in range(lo, hi):
+    u, part = divmod(idx, len(ranges))
+    b, hk = divmod(u, kv_heads)
+    pieces.append(RowPiece(b, hk, ranges[part][0], ranges[part][1]))
+  return pieces
+
+
+def run_row_sharded(fn, q, k, v, world: int, rank: int, causal: bool = True, window: int = 0):
+  """Runs `fn(q_piece, k_piece, v_piece)` -- the plain attention with the same causal / window arguments -- on this
+  rank's (unit, row range) pieces; every piece is a view (no copy).  Returns a list of (piece, result); result rows
+  are the piece's query rows, heads its unit's query heads."""
+  group = q.size(2) // k.size(2)
+  out = []
+  for pc in row_shard_pieces(q.size(0), k.size(2), q.size(1), k.size(1), world, rank, causal, window):
+    qs, ks, vs = slice_rows(q[pc.b:pc.b + 1, :, pc.hk * group:(pc.hk + 1) * group], k[pc.b:pc.b + 1, :, pc.hk:pc.hk + 1],
+                            v[pc.b:pc.b + 1, :, pc.hk:pc.hk + 1], pc.r0, pc.r1, causal)
+    out.append((pc, fn(qs, ks, vs)))
   return out
 
 

@@ -307,3 +307,26 @@ def test_head_sliced_views_give_the_bits_of_the_full_problem(cuda_device):
   for rank in range(world):
     for piece, out in sh.run_sharded(lambda a, b, c: att.attn_fwd(a, b, c), q, k, v, world, rank, dense=False):
       assert torch.equal(out[0], full[piece.b, :, piece.hk_lo * 3:piece.hk_hi * 3])
+
+
+@pytest.mark.parametrize("shape,opt", [((1, 2048, 2048, 4, 2, 256), {"window": 1024, "softcap": 50.0}),
+                                       ((2, 1024, 1536, 6, 3, 128), {}),
+                                       ((1, 1152, 1152, 2, 2, 128), {"window": 300})])
+def test_query_row_shards_give_the_bits_of_the_full_problem(cuda_device, shape, opt):
+  # problems with fewer (batch, kv-head) units than GPUs are also cut along their query rows, on tile boundaries,
+  # every piece a view of the full tensors with the keys its rows can see: same tiles, same key blocks, same bits
+  from deepgengraph_b200 import sharding as sh
+  B, Sq, Skv, H, Hk, D = shape
+  q, k, v = (t.to(cuda_device) for t in _qkv(B, Sq, Skv, H, Hk, D, torch.bfloat16, seed=131))
+  window = opt.get("window", 0)
+  full = att.attn_fwd(q, k, v, **opt)
+  world = 4 * B * Hk
+  got = torch.full_like(full, float("nan"))
+  g = H // Hk
+  n_pieces = 0
+  for rank in range(world):
+    for pc, out in sh.run_row_sharded(lambda a, b, c: att.attn_fwd(a, b, c, **opt), q, k, v, world, rank, True, window):
+      got[pc.b, pc.r0:pc.r1, pc.hk * g:(pc.hk + 1) * g] = out[0]
+      n_pieces += 1
+  assert n_pieces > B * Hk
+  assert torch.equal(got, full)

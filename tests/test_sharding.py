@@ -133,3 +133,57 @@ def test_failed_or_absent_rank_is_reported_without_a_collective(tmp_path, mode, 
   else:
     assert got[1] == "left" and got[0].startswith("peer_failure:failed=[]:missing=[1]"), got
     assert float(got[0].rsplit(":", 1)[1][:-1]) < 2.5, got   # reported at the time limit, not when the rank left
+
+
+@pytest.mark.parametrize("args", [(8192, 8192, 4, True, 4096), (8192, 8192, 2, True, 0), (1000, 1500, 3, True, 0),
+                                  (300, 300, 8, True, 0), (4096, 4096, 4, False, 0), (128, 128, 4, True, 0),
+                                  (4096, 4096, 3, True, 700)])
+def test_row_ranges_cover_the_rows_on_tile_boundaries_with_balanced_work(args):
+  q_len, kv_len, parts, causal, window = args
+  ranges = sh.row_ranges(q_len, kv_len, parts, causal, window)
+  assert ranges[0][0] == 0 and ranges[-1][1] == q_len and len(ranges) <= parts
+  for (a0, a1), (b0, b1) in zip(ranges, ranges[1:]):
+    assert a1 == b0
+  assert all(r0 % 128 == 0 and r1 > r0 for r0, r1 in ranges)
+  delta = kv_len - q_len
+
+  def visible(i):
+    hi = min(i + delta, kv_len - 1) if causal else kv_len - 1
+    lo = max(0, i + delta - window + 1) if (causal and window > 0) else 0
+    return hi - lo + 1
+  work = [sum(visible(i) for i in range(r0, r1)) for r0, r1 in ranges]
+  if len(ranges) == parts and q_len >= 16 * 128 * parts:   # enough tiles per part for the greedy cut to balance
+    assert max(work) <= 1.15 * sum(work) / parts
+
+
+def test_row_shard_pieces_partition_the_problem():
+  batch, kv_heads, q_len, kv_len = 1, 8, 8192, 8192      # config 5: eight units
+  for world in (1, 2, 8, 16, 24, 32):
+    seen = []
+    for rank in range(world):
+      seen += sh.row_shard_pieces(batch, kv_heads, q_len, kv_len, world, rank, True, 4096)
+    rows = {}
+    for pc in seen:
+      rows.setdefault((pc.b, pc.hk), []).append((pc.r0, pc.r1))
+    assert len(rows) == batch * kv_heads
+    for spans in rows.values():
+      spans.sort()
+      assert spans[0][0] == 0 and spans[-1][1] == q_len
+      assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+    if world >= 16:
+      assert all(len(sh.row_shard_pieces(batch, kv_heads, q_len, kv_len, world, r, True, 4096)) >= 1 for r in range(world - world % 8))
+
+
+def test_slice_rows_keeps_the_mask_alignment():
+  import torch
+  from oracle import reference_math as rm
+  g = torch.Generator().manual_seed(5)
+  q = torch.randn(1, 384, 2, 16, generator=g)
+  k = torch.randn(1, 512, 1, 16, generator=g)
+  v = torch.randn(1, 512, 1, 16, generator=g)
+  for window in (0, 100):
+    full = rm.attention_ref(q, k, v, causal=True, window=window)["out"]
+    for r0, r1 in ((0, 128), (128, 384), (256, 384)):
+      qs, ks, vs = sh.slice_rows(q, k, v, r0, r1, causal=True)
+      part = rm.attention_ref(qs, ks, vs, causal=True, window=window)["out"]
+      torch.testing.assert_close(part, full[:, r0:r1], rtol=1e-6, atol=1e-6)
