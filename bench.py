@@ -323,7 +323,7 @@ def sub_records(dev, peaks, iters, warmup):
     own time per launch, `us_median` stays the eager call through the Python API."""
     n_sets = len(fns) if isinstance(fns, list) else 1
     # Every record starts from an idle GPU, as the headline's timed region does: looping for seconds these kernels
-    # run into the board's power cap and the SM clock settles 10-25 % lower (the sustained figures are in DESIGN.md).
+    # run into the board's power cap and the SM clock settles 10-25 % lower.
     torch.cuda.synchronize()
     time.sleep(SUB_IDLE_S)
     med, mn = time_op(fns, iters, warmup)
