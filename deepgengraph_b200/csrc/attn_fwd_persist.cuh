@@ -234,8 +234,11 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         }
       }
       const int last = g - 1;
+      // (tuning builds: slots (3 * 64 + 48 + tile) * 8 + {0: last P delivered, 1: last P V complete, 2: output stored})
+      if (threadIdx.x == 0 && k < 8) B200_TL((3 * 64 + 48 + k) * 8 + 0);
       if (!mbar_wait(o_full + (last & 1), (last >> 1) & 1, c.abort_flag, WAIT_O_FULL)) break;
       tc_fence_after();
+      if (threadIdx.x == 0 && k < 8) B200_TL((3 * 64 + 48 + k) * 8 + 1);
       const float inv_l = 1.0f / l;
       const bool in_range = row < p.q_len;
       const bool wide_stores = (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
@@ -265,6 +268,7 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         }
       }
       if (p.lse != nullptr && in_range) p.lse[((int64_t)t.b * p.heads + t.h) * p.lse_stride + row] = m + log2f(l);
+      if (threadIdx.x == 0 && k < 8) B200_TL((3 * 64 + 48 + k) * 8 + 2);
       blocks_done = g;
     }
   } else if (warp == PRODUCER_WARP) {
