@@ -249,6 +249,7 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         uint32_t o[32];
         tmem_ld32(o_addr + ch * 32, o);
         tmem_ld_wait();
+        if (threadIdx.x == 0 && k < 8 && ch < 4) B200_TL((3 * 64 + 48 + k) * 8 + 3 + ch);   // chunk ch loaded
         if (in_range) {
           // every lane writes its own row (rows are heads * D elements apart), so a store instruction costs one
           // memory transaction per lane whatever its width: 32-byte stores halve the count
