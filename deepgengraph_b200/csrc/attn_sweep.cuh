@@ -669,6 +669,8 @@ attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   if (threadIdx.x == 0) status_now = *reinterpret_cast<volatile int*>(&g_device_status);
 
   B200_TL_INIT();
+  [[maybe_unused]] const uint64_t cta_start_ns = global_timer_ns();
+  [[maybe_unused]] const long long cta_start_clk = clock64();
   SweepCtx<Cfg> c;
   c.sA = smem;
   c.sX = c.sA + Cfg::A_BYTES;
@@ -785,6 +787,7 @@ attn_sweep_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   __syncthreads();
   if (warp == 0) tmem_dealloc(c.tmem_base, Cfg::TMEM_COLS);
   B200_TL_FLUSH();
+  B200_TL_CTA(cta_start_ns, cta_start_clk, c.blk_hi - c.blk_lo);
 }
 
 // Adds the per-chunk partial vectors in chunk order: out[bh][j] = mul * sum_c partial[bh][c][j].
